@@ -1,0 +1,366 @@
+// Flash-attention forward for sm_100a: S = Q K^T and O += P V on tcgen05 tensor cores with S, P and O
+// resident in tensor memory; K/V tiles streamed by TMA (no multicast) through a 2-stage ring; online
+// softmax with lazy rescaling in four softmax warps (one thread per query row).
+//
+// One kernel serves every attention mode of the framework:
+//   * local causal / non-causal attention with GQA (Ulysses, world size 1);
+//   * ring attention over a K/V buffer laid out in GLOBAL position order, masking on global
+//     positions (q_pos[] gives each local query row its global position), which replaces the
+//     reference's per-step Full / KHeadHalf / QTailHalf sub-chunk slicing and its separate
+//     online-softmax merge (context_parallel/ContextParallel.h:730-784,
+//     context_parallel/SDPAMerger.h:108-121): (m, l, O) simply persist across K/V blocks;
+//   * the fused ring: K/V blocks owned by other ranks arrive in the local buffer while the kernel
+//     runs; before the first tile of block c the loader waits (bounded) on ready[c].
+//
+// Tensors are token-major: Q [B,Tq,Hq,D], K/V [B,Tk,Hkv,D] with arbitrary 16-byte-aligned strides (views
+// into a packed QKV buffer work without a copy), O [B,Tq,Hq,D] contiguous, LSE [B,Hq,Tq] fp32 (natural log).
+//
+// Replaces fused_attn_forward_kernel_tc (context_parallel/AttentionForward.cu:490-844) and
+// gqa_fused_rope_v2 (context_parallel/GQA_fused_fwd_sm103_cp.cu:117-281).
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace cpb {
+
+constexpr int FA_BQ = 128;
+constexpr int FA_BK = 128;
+constexpr int FA_THREADS = 192;
+constexpr int FA_STAGES = 2;
+
+struct FwdParams {
+  int B, Tq, Tk, Hq, Hkv;
+  int causal;
+  int k_off;                 // global position of K row 0
+  float scale_log2;          // softmax scale * log2(e)
+  const int* q_pos;          // [Tq] global position of each query row, or null (= row index)
+  __nv_bfloat16* O;          // [B,Tq,Hq,D]
+  float* lse;                // [B,Hq,Tq]
+  // fused-ring readiness flags: K/V rows [c*block_rows, (c+1)*block_rows) may be read once
+  // ready[c] >= ready_epoch.  null -> everything is ready.
+  const int* ready;
+  int ready_epoch;
+  int block_rows;
+  int* status;
+};
+
+template <int D>
+struct FwdSmem {
+  static constexpr int Q_BYTES = FA_BQ * D * 2;
+  static constexpr int KV_BYTES = FA_BK * D * 2;
+  static constexpr int K_OFF = Q_BYTES;
+  static constexpr int V_OFF = K_OFF + FA_STAGES * KV_BYTES;
+  static constexpr int BAR_OFF = V_OFF + FA_STAGES * KV_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+// Bounded acquire-spin on a readiness flag in global memory (written by a copy kernel or a peer).
+__device__ __forceinline__ bool wait_flag_ge(const int* flag, int value, volatile int* abort_flag, int* status, int site) {
+  for (uint32_t it = 0; it < (1u << 22); ++it) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= value) return true;
+    if (*abort_flag) return false;
+    __nanosleep(200);
+  }
+  *abort_flag = 1;
+  report(status, ST_TIMEOUT_FLAG, site, value);
+  return false;
+}
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, (D == 64 ? 2 : 1))
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, FwdParams p) {
+  using L = FwdSmem<D>;
+  constexpr int DH = D / 64;                // 64-wide halves of the head dimension
+  constexpr uint32_t TMEM_COLS = 256;
+  constexpr uint32_t O_COL = 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + L::BAR_OFF);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;              // [2]
+  uint64_t* v_full = bars + 3;              // [2]
+  uint64_t* kv_empty = bars + 5;            // [2]
+  uint64_t* s_full = bars + 7;
+  uint64_t* p_full = bars + 8;
+  uint64_t* o_done = bars + 9;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.Hq / p.Hkv;
+  const int num_q_tiles = (p.Tq + FA_BQ - 1) / FA_BQ;
+  const int qt = num_q_tiles - 1 - (int)(blockIdx.x / G);     // heaviest tiles first
+  const int hkv = blockIdx.y;
+  const int hq = hkv * G + (int)(blockIdx.x % G);
+  const int b = blockIdx.z;
+  const int q0 = qt * FA_BQ;
+
+  // Range of K/V tiles this query tile attends to.
+  const int q_last = min(q0 + FA_BQ, p.Tq) - 1;
+  const int qpos_min = p.q_pos ? p.q_pos[q0] : q0;
+  const int qpos_max = p.q_pos ? p.q_pos[q_last] : q_last;
+  int n_kv = (p.Tk + FA_BK - 1) / FA_BK;
+  if (p.causal) {
+    const int last_idx = qpos_max - p.k_off;                  // last visible K index
+    n_kv = last_idx < 0 ? 0 : min(n_kv, last_idx / FA_BK + 1);
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA loader
+    if (lane == 0 && n_kv > 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, L::Q_BYTES);
+#pragma unroll
+      for (int h = 0; h < DH; ++h) tma_load_4d(smem + h * (FA_BQ * 128), &tmQ, q_full, h * 64, hq, q0, b);
+      int ready_block = -1;
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, p.status, 500)) break;
+        const int k0 = j * FA_BK;
+        if (p.ready != nullptr) {
+          // a tile may straddle two blocks when block_rows is not a multiple of the tile
+          const int blk_hi = min(k0 + FA_BK, p.Tk) - 1;
+          for (int c = max(ready_block + 1, k0 / p.block_rows); c <= blk_hi / p.block_rows; ++c) {
+            if (!wait_flag_ge(p.ready + c, p.ready_epoch, abort_flag, p.status, 501)) break;
+            ready_block = c;
+          }
+          if (*abort_flag) break;
+        }
+        uint8_t* sk = smem + L::K_OFF + st * L::KV_BYTES;
+        uint8_t* sv = smem + L::V_OFF + st * L::KV_BYTES;
+        mbar_expect_tx(&k_full[st], L::KV_BYTES);
+#pragma unroll
+        for (int h = 0; h < DH; ++h) tma_load_4d(sk + h * (FA_BK * 128), &tmK, &k_full[st], h * 64, hkv, k0, b);
+        mbar_expect_tx(&v_full[st], L::KV_BYTES);
+#pragma unroll
+        for (int h = 0; h < DH; ++h) tma_load_4d(sv + h * (FA_BK * 128), &tmV, &v_full[st], h * 64, hkv, k0, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(FA_BQ, FA_BK, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(FA_BQ, D, false, true);
+      const uint32_t sq = smem_u32(smem);
+      const uint32_t s_tmem = tmem_base;
+      const uint32_t o_tmem = tmem_base + O_COL;
+      auto issue_qk = [&](int j) {
+        const uint32_t sk = smem_u32(smem + L::K_OFF + (j & 1) * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * (FA_BQ * 128) + (k % 4) * 32;
+          umma_ss(s_tmem, sdesc_kmajor(sq + off), sdesc_kmajor(sk + off), idesc_qk, k != 0);
+        }
+        umma_commit(s_full);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 600) && mbar_wait(&k_full[0], 0, abort_flag, p.status, 601);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0);
+        for (int j = 0; j < n_kv; ++j) {
+          const int st = j & 1;
+          if (!mbar_wait(p_full, j & 1, abort_flag, p.status, 602)) break;
+          if (!mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, p.status, 603)) break;
+          tc_fence_after();
+          const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
+#pragma unroll
+          for (int k = 0; k < FA_BK / 16; ++k) {
+            // A = P (bf16, 8 tensor-memory columns per 16 keys); B = V tile, N-major: 16 key rows = 2 KB
+            umma_ts(o_tmem, s_tmem + k * 8, make_sdesc(sv + k * 2048, FA_BK * 128, 1024), idesc_pv, (j | k) != 0);
+          }
+          umma_commit(&kv_empty[st]);
+          if (j + 1 < n_kv) {
+            if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 604)) break;
+            tc_fence_after();
+            issue_qk(j + 1);
+          } else {
+            umma_commit(o_done);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int qi = q0 + row;
+    const bool row_valid = qi < p.Tq;
+    const int my_qpos = row_valid ? (p.q_pos ? p.q_pos[qi] : qi) : 0x7fffffff;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float m_used = -INFINITY;    // running max (scaled, log2 domain) the accumulators are relative to
+    float l = 0.f;
+    bool alive = n_kv > 0;
+    for (int j = 0; j < n_kv && alive; ++j) {
+      bool ok = mbar_wait(s_full, j & 1, abort_flag, p.status, 700);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { alive = false; break; }
+      tc_fence_after();
+      const int k0 = j * FA_BK;
+      const bool need_mask = (k0 + FA_BK > p.Tk) || (p.causal && (k0 + FA_BK - 1 + p.k_off > qpos_min));
+      const int kmax_causal = p.causal ? (my_qpos - p.k_off) : 0x7fffffff;   // last visible index
+      const int kmax = min(kmax_causal, p.Tk - 1) - k0;                       // last visible column of this tile
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < FA_BK; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(t_lane + c, v);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (c + i <= kmax) mx = fmaxf(mx, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+      }
+      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      // lazy rescale: keep the old reference maximum unless it fell behind by more than 2^8
+      const bool need = (m_new > m_used + 8.f);
+      float alpha = 1.f;
+      if (need) {
+        alpha = (m_used == -INFINITY) ? 0.f : ex2f(m_used - m_new);
+        m_used = m_new;
+        l *= alpha;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(t_lane + O_COL + c, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st32(t_lane + O_COL + c, v);
+        }
+      }
+      // pass 2: p = exp2(s*scale - m), row sum, bf16 P written behind the S columns already consumed
+      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+#pragma unroll 1
+      for (int c = 0; c < FA_BK; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(t_lane + c, v);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = ex2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_sub));
+          float p1 = ex2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_sub));
+          if (need_mask) {
+            if (c + i > kmax) p0 = 0.f;
+            if (c + i + 1 > kmax) p1 = 0.f;
+          }
+          l += p0 + p1;
+          pk[i >> 1] = pack_bf16(p0, p1);
+        }
+        tmem_st16(t_lane + (c >> 1), pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    // epilogue: O / l -> bf16, LSE
+    if (alive) {
+      bool ok = mbar_wait(o_done, 0, abort_flag, p.status, 701);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        const float inv_l = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* orow = p.O + (((size_t)b * p.Tq + (row_valid ? qi : 0)) * p.Hq + hq) * D;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(t_lane + O_COL + c, v);
+          tmem_wait_ld();
+          if (row_valid) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(v[i]) * inv_l, __uint_as_float(v[i + 1]) * inv_l);
+              o.y = pack_bf16(__uint_as_float(v[i + 2]) * inv_l, __uint_as_float(v[i + 3]) * inv_l);
+              o.z = pack_bf16(__uint_as_float(v[i + 4]) * inv_l, __uint_as_float(v[i + 5]) * inv_l);
+              o.w = pack_bf16(__uint_as_float(v[i + 6]) * inv_l, __uint_as_float(v[i + 7]) * inv_l);
+              *(uint4*)(orow + c + i) = o;
+            }
+          }
+        }
+        if (row_valid)
+          p.lse[((size_t)b * p.Hq + hq) * p.Tq + qi] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      }
+    } else if (n_kv == 0 && row_valid) {
+      // no visible key at all: zero output, LSE = -inf
+      __nv_bfloat16* orow = p.O + (((size_t)b * p.Tq + qi) * p.Hq + hq) * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 8) *(uint4*)(orow + c) = make_uint4(0, 0, 0, 0);
+      p.lse[((size_t)b * p.Hq + hq) * p.Tq + qi] = -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+static int make_qkv_tmap(CUtensorMap* m, const void* ptr, int D, int H, int T, int B, long s_head, long s_tok,
+                         long s_batch, int box_rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)T, (uint64_t)B};
+  uint64_t strides[4] = {0, (uint64_t)s_head * 2, (uint64_t)s_tok * 2, (uint64_t)s_batch * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
+  return encode_tmap(m, ptr, 2, 4, dims, strides, box, 1);
+}
+
+}  // namespace cpb
+
+using namespace cpb;
+
+// strides are in elements: (head, token, batch) for q and for k/v (k and v share strides).
+extern "C" int cpb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                             int B, int Tq, int Tk, int Hq, int Hkv, int D,
+                             long q_sh, long q_st, long q_sb, long k_sh, long k_st, long k_sb,
+                             float scale, int causal, int k_off, const int* q_pos,
+                             const int* ready, int ready_epoch, int block_rows, int* status, cudaStream_t stream) {
+  if (D != 64 && D != 128) return set_error(CPB_ERR_ARG, "flash_fwd: head_dim %d not in {64,128}", D);
+  if (Hq % Hkv) return set_error(CPB_ERR_ARG, "flash_fwd: Hq %% Hkv != 0");
+  if (B <= 0 || Tq <= 0 || Tk <= 0) return set_error(CPB_ERR_ARG, "flash_fwd: empty problem");
+  if (ready != nullptr && block_rows <= 0) return set_error(CPB_ERR_ARG, "flash_fwd: block_rows must be positive with ready flags");
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_qkv_tmap(&tq, q, D, Hq, Tq, B, q_sh, q_st, q_sb, FA_BQ)) != CPB_OK) return rc;
+  if ((rc = make_qkv_tmap(&tk, k, D, Hkv, Tk, B, k_sh, k_st, k_sb, FA_BK)) != CPB_OK) return rc;
+  if ((rc = make_qkv_tmap(&tv, v, D, Hkv, Tk, B, k_sh, k_st, k_sb, FA_BK)) != CPB_OK) return rc;
+  FwdParams p;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.k_off = k_off;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.q_pos = q_pos; p.O = (__nv_bfloat16*)o; p.lse = lse;
+  p.ready = ready; p.ready_epoch = ready_epoch; p.block_rows = block_rows; p.status = status;
+  const int G = Hq / Hkv;
+  dim3 grid(((Tq + FA_BQ - 1) / FA_BQ) * G, Hkv, B);
+  if (D == 64) {
+    static bool cfg = false;
+    if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::TOTAL)); cfg = true; }
+    flash_fwd_kernel<64><<<grid, FA_THREADS, FwdSmem<64>::TOTAL, stream>>>(tq, tk, tv, p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::TOTAL)); cfg = true; }
+    flash_fwd_kernel<128><<<grid, FA_THREADS, FwdSmem<128>::TOTAL, stream>>>(tq, tk, tv, p);
+  }
+  return check_launch("flash_fwd");
+}

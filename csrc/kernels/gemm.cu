@@ -1,0 +1,349 @@
+// Persistent bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma -> tensor memory ->
+// registers -> global, warp-specialised, with a double-buffered accumulator so the epilogue of tile
+// i overlaps the main loop of tile i+1.
+//
+//   C[M,N] (op)= A * B        A is M x K, B is N x K ("NT": both K-major) by default.
+//   a_mn = 1 : A is stored as [K, M] (M contiguous)   -> weight-gradient GEMM  dW = dY^T X
+//   b_mn = 1 : B is stored as [K, N] (N contiguous)   -> data-gradient GEMM    dX = dY W
+// Both majors are native UMMA operand layouts, so no transposed copies are ever made.
+//
+// Replaces the cuBLAS GEMMs behind nn::Linear in the reference trainers
+// (Scripts/Blutrain/bluscriptCP.cpp:212-330, Makefile:129).
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = tensor-memory owner + MMA issuer,
+// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace cpb {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+enum : int {
+  EPI_BF16 = 0,        // C(bf16) = acc (+bias)
+  EPI_F32 = 1,         // C(f32)  = acc (+bias)
+  EPI_F32_ACC = 2,     // C(f32) += acc
+  EPI_BF16_GELU = 3,   // C(bf16) = gelu_tanh(acc + bias); aux(bf16) = acc + bias (pre-activation) when aux != null
+  EPI_BF16_SWIGLU = 4, // B tile = [gate rows | up rows]; C(bf16)[:, n] = silu(g)*u ; aux gets [g | u] when aux != null
+};
+
+struct GemmParams {
+  int M, N, K;
+  int ldc;             // elements
+  int ld_aux;
+  int epi;
+  int num_m_blocks, num_n_blocks, num_k_blocks;
+  int swiglu_half;     // number of output features F when epi == SWIGLU (B has 2F rows)
+  void* C;
+  void* aux;
+  const float* bias;
+  int* status;
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // barriers + alignment slack
+};
+
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  // tanh(u) = 1 - 2/(exp(2u)+1)
+  float e = __expf(2.f * u);
+  float t = 1.f - 2.f / (e + 1.f);
+  return 0.5f * x * (1.f + t);
+}
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  using L = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;     // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;         // [2]
+  uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&tfull_bar[s], 1); mbar_init(&tempty_bar[s], 4); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0; uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile / p.num_n_blocks) * GEMM_BM;
+        const int n0 = (tile % p.num_n_blocks) * BN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 100)) break;
+          uint8_t* sa = smem + stage * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          const int k0 = kb * GEMM_BK;
+          if (A_MN) {
+#pragma unroll
+            for (int g = 0; g < GEMM_BM / 64; ++g) tma_load_2d(sa + g * 8192, &tmA, &full_bar[stage], m0 + g * 64, k0);
+          } else {
+            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+          }
+          if (p.epi == EPI_BF16_SWIGLU) {
+            // gate rows n0/2.. and up rows F + n0/2.. of the fused [2F, K] weight
+            const int f0 = (tile % p.num_n_blocks) * (BN / 2);
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, f0);
+            tma_load_2d(sb + (BN / 2) * 128, &tmB, &full_bar[stage], k0, p.swiglu_half + f0);
+          } else if (B_MN) {
+#pragma unroll
+            for (int g = 0; g < BN / 64; ++g) tma_load_2d(sb + g * 8192, &tmB, &full_bar[stage], n0 + g * 64, k0);
+          } else {
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (*abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, A_MN, B_MN);
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 200)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201)) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t da = A_MN ? make_sdesc(sa + k * 2048, 8192, 1024) : sdesc_kmajor(sa + k * 32);
+            const uint64_t db = B_MN ? make_sdesc(sb + k * 2048, 8192, 1024) : sdesc_kmajor(sb + k * 32);
+            umma_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        umma_commit(&tfull_bar[acc]);
+        if (*abort_flag) break;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (tile / p.num_n_blocks) * GEMM_BM;
+      const int nb = tile % p.num_n_blocks;
+      const int n0 = nb * BN;
+      bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 300);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if (p.epi == EPI_BF16_SWIGLU) {
+        // accumulator columns [0, BN/2) = gate, [BN/2, BN) = up, for features f0..f0+BN/2
+        const int f0 = nb * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld32(t_row + c, g);
+          tmem_ld32(t_row + BN / 2 + c, u);
+          tmem_wait_ld();
+          if (row < p.M) {
+            __nv_bfloat16* crow = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + f0 + c;
+            __nv_bfloat16* arow = p.aux ? (__nv_bfloat16*)p.aux + (size_t)row * p.ld_aux : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (f0 + c + j < p.swiglu_half) {
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  float g0 = __uint_as_float(g[j + 2 * q]), g1 = __uint_as_float(g[j + 2 * q + 1]);
+                  float u0 = __uint_as_float(u[j + 2 * q]), u1 = __uint_as_float(u[j + 2 * q + 1]);
+                  o[q] = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
+                }
+                *(uint4*)(crow + j) = make_uint4(o[0], o[1], o[2], o[3]);
+                if (arow) {
+                  uint32_t pg[4], pu[4];
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    pg[q] = pack_bf16(__uint_as_float(g[j + 2 * q]), __uint_as_float(g[j + 2 * q + 1]));
+                    pu[q] = pack_bf16(__uint_as_float(u[j + 2 * q]), __uint_as_float(u[j + 2 * q + 1]));
+                  }
+                  *(uint4*)(arow + f0 + c + j) = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+                  *(uint4*)(arow + p.swiglu_half + f0 + c + j) = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+                }
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(t_row + c, v);
+          tmem_wait_ld();
+          const int col = n0 + c;
+          if (row < p.M && col < p.N) {
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col + j < p.N) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldg(p.bias + col + j));
+            }
+            if (p.epi == EPI_BF16 || p.epi == EPI_BF16_GELU) {
+              __nv_bfloat16* crow = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + col;
+              __nv_bfloat16* arow = (p.epi == EPI_BF16_GELU && p.aux) ? (__nv_bfloat16*)p.aux + (size_t)row * p.ld_aux + col : nullptr;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (col + j < p.N) {       // N is a multiple of 8
+                  uint32_t o[4];
+                  if (p.epi == EPI_BF16_GELU) {
+                    if (arow) {
+                      uint32_t a[4];
+#pragma unroll
+                      for (int q = 0; q < 4; ++q) a[q] = pack_bf16(__uint_as_float(v[j + 2 * q]), __uint_as_float(v[j + 2 * q + 1]));
+                      *(uint4*)(arow + j) = make_uint4(a[0], a[1], a[2], a[3]);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                      o[q] = pack_bf16(gelu_tanh_f(__uint_as_float(v[j + 2 * q])), gelu_tanh_f(__uint_as_float(v[j + 2 * q + 1])));
+                  } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) o[q] = pack_bf16(__uint_as_float(v[j + 2 * q]), __uint_as_float(v[j + 2 * q + 1]));
+                  }
+                  *(uint4*)(crow + j) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+              }
+            } else {
+              float* crow = (float*)p.C + (size_t)row * p.ldc + col;
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                if (col + j < p.N) {       // N is a multiple of 4 on this path
+                  float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                  if (p.epi == EPI_F32_ACC) {
+                    float4 old = *(float4*)(crow + j);
+                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                  }
+                  *(float4*)(crow + j) = o;
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  using L = GemmSmem<BN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    CPB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    configured = true;
+  }
+  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, p);
+  return check_launch("gemm_bf16");
+}
+
+}  // namespace cpb
+
+using namespace cpb;
+
+// A: bf16, [M,K] row stride lda (a_mn=0) or [K,M] row stride lda (a_mn=1).
+// B: bf16, [N,K] row stride ldb (b_mn=0) or [K,N] row stride ldb (b_mn=1).
+// epi: see EPI_* above.  For EPI_BF16_SWIGLU B is the fused [2F, K] weight, N = F output features.
+extern "C" int cpb_gemm_bf16(const void* A, const void* B, void* C, void* aux, const float* bias,
+                             int M, int N, int K, int lda, int ldb, int ldc, int ld_aux,
+                             int a_mn, int b_mn, int epi, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return set_error(CPB_ERR_ARG, "gemm: empty problem %dx%dx%d", M, N, K);
+  if ((K % 8) || (N % 8) || (lda % 8) || (ldb % 8)) return set_error(CPB_ERR_ARG, "gemm: K,N,lda,ldb must be multiples of 8 (got K=%d N=%d lda=%d ldb=%d)", K, N, lda, ldb);
+  if (a_mn && (M % 8)) return set_error(CPB_ERR_ARG, "gemm: M must be a multiple of 8 when A is M-major");
+  if (epi == EPI_BF16_SWIGLU && (a_mn || b_mn)) return set_error(CPB_ERR_ARG, "gemm: swiglu epilogue needs K-major operands");
+  const int BN = (epi == EPI_BF16_SWIGLU || N > 128) ? 256 : 128;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ld_aux = ld_aux; p.epi = epi;
+  p.num_m_blocks = (M + GEMM_BM - 1) / GEMM_BM;
+  p.num_k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+  p.swiglu_half = (epi == EPI_BF16_SWIGLU) ? N : 0;
+  p.num_n_blocks = (epi == EPI_BF16_SWIGLU) ? (N + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
+  p.C = C; p.aux = aux; p.bias = bias; p.status = status;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  {
+    uint64_t dims[2], strides[2]; uint32_t box[2];
+    if (a_mn) { dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 64; box[1] = GEMM_BK; }
+    else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = GEMM_BK; box[1] = GEMM_BM; }
+    strides[0] = 0; strides[1] = (uint64_t)lda * 2;
+    if ((rc = encode_tmap(&tmA, A, 2, 2, dims, strides, box, 1)) != CPB_OK) return rc;
+  }
+  {
+    uint64_t dims[2], strides[2]; uint32_t box[2];
+    const uint64_t b_rows = (epi == EPI_BF16_SWIGLU) ? (uint64_t)2 * N : (uint64_t)N;
+    if (b_mn) { dims[0] = b_rows; dims[1] = (uint64_t)K; box[0] = 64; box[1] = GEMM_BK; }
+    else      { dims[0] = (uint64_t)K; dims[1] = b_rows; box[0] = GEMM_BK; box[1] = (epi == EPI_BF16_SWIGLU) ? BN / 2 : BN; }
+    strides[0] = 0; strides[1] = (uint64_t)ldb * 2;
+    if ((rc = encode_tmap(&tmB, B, 2, 2, dims, strides, box, 1)) != CPB_OK) return rc;
+  }
+#define CPB_GEMM_DISPATCH(BN_, ST_)                                                      \
+  do {                                                                                   \
+    if (!a_mn && !b_mn) return launch_gemm<BN_, ST_, false, false>(tmA, tmB, p, stream);  \
+    if (!a_mn && b_mn) return launch_gemm<BN_, ST_, false, true>(tmA, tmB, p, stream);    \
+    if (a_mn && !b_mn) return launch_gemm<BN_, ST_, true, false>(tmA, tmB, p, stream);    \
+    return launch_gemm<BN_, ST_, true, true>(tmA, tmB, p, stream);                        \
+  } while (0)
+  if (BN == 256) CPB_GEMM_DISPATCH(256, 4);
+  CPB_GEMM_DISPATCH(128, 6);
+#undef CPB_GEMM_DISPATCH
+}
