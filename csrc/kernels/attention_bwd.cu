@@ -1,0 +1,432 @@
+// Flash-attention backward for sm_100a.  One CTA owns one 128-row K/V tile of one KV head and sweeps
+// every query tile (of every query head of the GQA group) that can see it, with all five products
+// on tcgen05 tensor cores and every accumulator in tensor memory:
+//
+//   S^T  = K Q^T            (smem x smem)          P^T  = exp2(S^T*c - LSE)         (registers)
+//   dP^T = V dO^T           (smem x smem)          dS^T = P^T o (dP^T - Delta) * scale
+//   dV  += P^T  dO          (tmem x smem)          dK  += dS^T Q      (tmem x smem)
+//   dQ   = dS K             (smem x smem, dS^T staged M-major in shared memory) -> fp32 red.add
+//
+// Computing the transposed score tile puts K/V rows in tensor-memory lanes, so P^T and dS^T feed the
+// dV / dK products directly as tensor-memory A operands and dK / dV never leave tensor memory until
+// the sweep ends.  dK/dV can be written as bf16 or accumulated into fp32 buffers (the ring calls the
+// kernel once per query shard and sums contributions, like the reference's travelling fp32
+// accumulator, context_parallel/ContextParallelBackward.h:151-158,546-627).  P is recomputed from the
+// merged LSE (context_parallel/AttentionBackward.cu:446).  Masking is on global positions, as in the
+// forward.
+//
+// Replaces mem_efficient_bwd_unified_kernel_exp11 (context_parallel/AttentionBackward.cu:300-541) and
+// gqa_fused_rope_bwd_dQ / _dKdV (context_parallel/GQA_fused_bwd_sm103_cp.cu:135-565).
+//
+// Warp roles (320 threads): 0 = TMA loader, 1 = MMA issuer, 2..5 = softmax-gradient warps (thread = K/V
+// row), 6..9 = dQ drain warps (thread = query row).
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace cpb {
+
+constexpr int FB_T = 128;            // tile edge (queries and keys)
+constexpr int FB_THREADS = 320;
+
+struct BwdParams {
+  int B, Tq, Tk, Hq, Hkv, Tq_pad;
+  int causal, k_off;
+  float scale, scale_log2;
+  const float* lse2;        // [B,Hq,Tq_pad] LSE * log2(e), +inf in the padding
+  const float* delta;       // [B,Hq,Tq_pad] rowsum(dO o O), 0 in the padding
+  const int* q_pos;         // [Tq_pad] global positions, INT_MAX in the padding
+  float* dq;                // [B,Tq,Hq,D] fp32, accumulated with red.add
+  void* dk; void* dv;       // [B,Tk,Hkv,D] bf16 (store) or fp32 (accumulate)
+  int dkv_f32_accumulate;
+  int* status;
+};
+
+template <int D>
+struct BwdSmem {
+  static constexpr int STAGES = (D == 64) ? 2 : 1;
+  static constexpr int TILE = FB_T * D * 2;
+  static constexpr int K_OFF = 0;
+  static constexpr int V_OFF = TILE;
+  static constexpr int Q_OFF = 2 * TILE;
+  static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
+  static constexpr int DS_OFF = DO_OFF + STAGES * TILE;           // dS^T: 128 x 128 bf16, M-major
+  static constexpr int VEC_OFF = DS_OFF + FB_T * FB_T * 2;        // per stage: lse2[128], delta[128], qpos[128]
+  static constexpr int BAR_OFF = VEC_OFF + STAGES * 3 * 512;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__device__ __forceinline__ void bulk_load_1d(void* smem, const void* gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem)), "l"((uint64_t)gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(FB_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, BwdParams p) {
+  using L = BwdSmem<D>;
+  constexpr int ST = L::STAGES;
+  constexpr int DH = D / 64;
+  constexpr uint32_t ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
+  constexpr uint32_t DQ_COL = (D == 64) ? 384 : 0;           // D=128: dQ reuses the S^T columns
+  constexpr bool DQ_ALIAS = (D != 64);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + L::BAR_OFF);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* q_full = bars + 1;        // [2]
+  uint64_t* q_empty = bars + 3;       // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_full = bars + 6;
+  uint64_t* dq_full = bars + 7;
+  uint64_t* dq_empty = bars + 8;
+  uint64_t* acc_done = bars + 9;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* qt_start_s = (int*)(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int k0 = kt * FB_T;
+  const int num_q_tiles = p.Tq_pad / FB_T;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    mbar_init(s_full, 1); mbar_init(p_full, 128); mbar_init(dq_full, 1); mbar_init(dq_empty, 128); mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    *qt_start_s = num_q_tiles;
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // First query tile that can see this K/V tile (q_pos is non-decreasing).
+  if (p.causal) {
+    const int kpos_min = p.k_off + k0;
+    for (int t = threadIdx.x; t < num_q_tiles; t += blockDim.x) {
+      const int last = min(t * FB_T + FB_T, p.Tq) - 1;
+      if (p.q_pos[last] >= kpos_min) { atomicMin(qt_start_s, t); break; }
+    }
+  } else if (threadIdx.x == 0) {
+    *qt_start_s = 0;
+  }
+  __syncthreads();
+  const int qt_start = *qt_start_s;
+  const int n_qt = num_q_tiles - qt_start;
+  const int n_it = n_qt * G;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA loader
+    if (lane == 0 && n_it > 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(kv_full, 2 * L::TILE);
+#pragma unroll
+      for (int h = 0; h < DH; ++h) {
+        tma_load_4d(smem + L::K_OFF + h * (FB_T * 128), &tmK, kv_full, h * 64, hkv, k0, b);
+        tma_load_4d(smem + L::V_OFF + h * (FB_T * 128), &tmV, kv_full, h * 64, hkv, k0, b);
+      }
+      for (int i = 0; i < n_it; ++i) {
+        const int st = i % ST;
+        const uint32_t ph = (i / ST) & 1;
+        if (!mbar_wait(&q_empty[st], ph ^ 1, abort_flag, p.status, 800)) break;
+        const int hq = hkv * G + i / n_qt;
+        const int q0 = (qt_start + i % n_qt) * FB_T;
+        mbar_expect_tx(&q_full[st], 2 * L::TILE + 3 * 512);
+#pragma unroll
+        for (int h = 0; h < DH; ++h) {
+          tma_load_4d(smem + L::Q_OFF + st * L::TILE + h * (FB_T * 128), &tmQ, &q_full[st], h * 64, hq, q0, b);
+          tma_load_4d(smem + L::DO_OFF + st * L::TILE + h * (FB_T * 128), &tmDO, &q_full[st], h * 64, hq, q0, b);
+        }
+        uint8_t* vec = smem + L::VEC_OFF + st * 1536;
+        const size_t row_off = ((size_t)b * p.Hq + hq) * p.Tq_pad + q0;
+        bulk_load_1d(vec, p.lse2 + row_off, 512, &q_full[st]);
+        bulk_load_1d(vec + 512, p.delta + row_off, 512, &q_full[st]);
+        bulk_load_1d(vec + 1024, p.q_pos + q0, 512, &q_full[st]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(FB_T, FB_T, false, false);     // S^T, dP^T
+      constexpr uint32_t idesc_acc = make_idesc_bf16(FB_T, D, false, true);        // dV, dK: A in tmem, B N-major
+      constexpr uint32_t idesc_dq = make_idesc_bf16(FB_T, D, true, true);          // dQ: A M-major smem, B N-major
+      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF), sDS = smem_u32(smem + L::DS_OFF);
+      if (mbar_wait(kv_full, 0, abort_flag, p.status, 900)) {
+        for (int i = 0; i < n_it; ++i) {
+          const int st = i % ST;
+          const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE), sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
+          if (!mbar_wait(&q_full[st], (i / ST) & 1, abort_flag, p.status, 901)) break;
+          if (DQ_ALIAS && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 902)) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k / 4) * (FB_T * 128) + (k % 4) * 32;
+            umma_ss(tmem_base + ST_COL, sdesc_kmajor(sK + off), sdesc_kmajor(sQ + off), idesc_s, k != 0);
+          }
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k / 4) * (FB_T * 128) + (k % 4) * 32;
+            umma_ss(tmem_base + DPT_COL, sdesc_kmajor(sV + off), sdesc_kmajor(sDO + off), idesc_s, k != 0);
+          }
+          umma_commit(s_full);
+          if (!mbar_wait(p_full, i & 1, abort_flag, p.status, 903)) break;
+          if (!DQ_ALIAS && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 904)) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < FB_T / 16; ++k)      // dV += P^T dO : contraction over the 128 queries
+            umma_ts(tmem_base + DV_COL, tmem_base + ST_COL + k * 8, make_sdesc(sDO + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
+#pragma unroll
+          for (int k = 0; k < FB_T / 16; ++k)      // dK += dS^T Q
+            umma_ts(tmem_base + DK_COL, tmem_base + DPT_COL + k * 8, make_sdesc(sQ + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
+#pragma unroll
+          for (int k = 0; k < FB_T / 16; ++k)      // dQ = dS K : contraction over the 128 keys
+            umma_ss(tmem_base + DQ_COL, make_sdesc(sDS + k * 2048, FB_T * 128, 1024), make_sdesc(sK + k * 2048, FB_T * 128, 1024), idesc_dq, k != 0);
+          umma_commit(&q_empty[st]);
+          umma_commit(dq_full);
+        }
+        umma_commit(acc_done);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ softmax-gradient warps
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                  // K/V row inside the tile
+    const int kidx = k0 + r;
+    const bool k_valid = kidx < p.Tk;
+    const int kpos = p.k_off + kidx;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    uint8_t* ds_row = smem + L::DS_OFF + r * 128;
+    bool alive = true;
+    for (int i = 0; i < n_it && alive; ++i) {
+      const int st = i % ST;
+      bool ok = mbar_wait(&q_full[st], (i / ST) & 1, abort_flag, p.status, 1000) &&
+                mbar_wait(s_full, i & 1, abort_flag, p.status, 1001);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { alive = false; break; }
+      tc_fence_after();
+      const float* lse2 = (const float*)(smem + L::VEC_OFF + st * 1536);
+      const float* delta = lse2 + 128;
+      const int* qpos = (const int*)(lse2 + 256);
+      const bool need_mask = p.causal && (p.k_off + k0 + FB_T - 1 > qpos[0]);
+#pragma unroll 1
+      for (int c = 0; c < FB_T; c += 32) {
+        uint32_t s[32], dp[32];
+        tmem_ld32(t_lane + ST_COL + c, s);
+        tmem_ld32(t_lane + DPT_COL + c, dp);
+        tmem_wait_ld();
+        uint32_t pk[16], dk_[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p0 = ex2f(fmaf(__uint_as_float(s[j]), p.scale_log2, -lse2[c + j]));
+          float p1 = ex2f(fmaf(__uint_as_float(s[j + 1]), p.scale_log2, -lse2[c + j + 1]));
+          if (!k_valid) { p0 = 0.f; p1 = 0.f; }
+          if (need_mask) {
+            if (kpos > qpos[c + j]) p0 = 0.f;
+            if (kpos > qpos[c + j + 1]) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(dp[j]) - delta[c + j]) * p.scale;
+          const float d1 = p1 * (__uint_as_float(dp[j + 1]) - delta[c + j + 1]) * p.scale;
+          pk[j >> 1] = pack_bf16(p0, p1);
+          dk_[j >> 1] = pack_bf16(d0, d1);
+        }
+        tmem_st16(t_lane + ST_COL + (c >> 1), pk);
+        tmem_st16(t_lane + DPT_COL + (c >> 1), dk_);
+        // dS^T row r, queries c..c+31 -> shared memory, M-major 128B-swizzled: 16-byte chunk q/8 of the
+        // 64-query group q/64 goes to chunk position (chunk ^ (r & 7)).
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int q = c + ch * 8;
+          const int grp = q >> 6, chunk = (q & 63) >> 3;
+          uint4 val = make_uint4(dk_[ch * 4], dk_[ch * 4 + 1], dk_[ch * 4 + 2], dk_[ch * 4 + 3]);
+          *(uint4*)(ds_row + grp * (FB_T * 128) + ((chunk ^ (r & 7)) << 4)) = val;
+        }
+      }
+      tmem_wait_st();
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    // final: dK, dV -> global
+    if (n_it == 0) {
+      if (!p.dkv_f32_accumulate && k_valid) {
+        __nv_bfloat16* dkr = (__nv_bfloat16*)p.dk + (((size_t)b * p.Tk + kidx) * p.Hkv + hkv) * D;
+        __nv_bfloat16* dvr = (__nv_bfloat16*)p.dv + (((size_t)b * p.Tk + kidx) * p.Hkv + hkv) * D;
+#pragma unroll
+        for (int c = 0; c < D; c += 8) { *(uint4*)(dkr + c) = make_uint4(0, 0, 0, 0); *(uint4*)(dvr + c) = make_uint4(0, 0, 0, 0); }
+      }
+    } else if (alive) {
+      bool ok = mbar_wait(acc_done, 0, abort_flag, p.status, 1002);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        const size_t off = (((size_t)b * p.Tk + (k_valid ? kidx : 0)) * p.Hkv + hkv) * D;
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t col = which ? DV_COL : DK_COL;
+          void* base = which ? p.dv : p.dk;
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(t_lane + col + c, v);
+            tmem_wait_ld();
+            if (k_valid) {
+              if (p.dkv_f32_accumulate) {
+                float* dst = (float*)base + off + c;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                  float4 o = *(float4*)(dst + j);
+                  o.x += __uint_as_float(v[j]); o.y += __uint_as_float(v[j + 1]);
+                  o.z += __uint_as_float(v[j + 2]); o.w += __uint_as_float(v[j + 3]);
+                  *(float4*)(dst + j) = o;
+                }
+              } else {
+                __nv_bfloat16* dst = (__nv_bfloat16*)base + off + c;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 o;
+                  o.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                  o.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                  o.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                  o.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                  *(uint4*)(dst + j) = o;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ dQ drain warps (6..9)
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                  // query row inside the tile
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    for (int i = 0; i < n_it; ++i) {
+      bool ok = mbar_wait(dq_full, i & 1, abort_flag, p.status, 1100);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int hq = hkv * G + i / n_qt;
+      const int qi = (qt_start + i % n_qt) * FB_T + r;
+      float* dst = p.dq + (((size_t)b * p.Tq + (qi < p.Tq ? qi : 0)) * p.Hq + hq) * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(t_lane + DQ_COL + c, v);
+        tmem_wait_ld();
+        if (qi < p.Tq) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            red_add_v4(dst + c + j, __uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_empty);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// delta[b,h,t] = sum_d dO*O ; lse2 = lse*log2(e) ; padding rows get delta 0 / lse2 +inf.  One warp per row.
+template <int D>
+__global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2,
+                                int B, int Tq, int Hq, int Tq_pad) {
+  const int lane = threadIdx.x & 31;
+  const size_t nrow = (size_t)B * Hq * Tq_pad;
+  for (size_t w = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); w < nrow; w += (size_t)gridDim.x * (blockDim.x >> 5)) {
+    const int t = (int)(w % Tq_pad);
+    const int h = (int)((w / Tq_pad) % Hq);
+    const int b = (int)(w / ((size_t)Tq_pad * Hq));
+    if (t >= Tq) {
+      if (lane == 0) { delta[w] = 0.f; lse2[w] = INFINITY; }
+      continue;
+    }
+    const size_t off = (((size_t)b * Tq + t) * Hq + h) * D;
+    float s = 0.f;
+#pragma unroll
+    for (int e = lane * 2; e < D; e += 64) {
+      const uint32_t a = *(const uint32_t*)(o + off + e), g = *(const uint32_t*)(dout + off + e);
+      s += bf16_lo(a) * bf16_lo(g) + bf16_hi(a) * bf16_hi(g);
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+    if (lane == 0) {
+      delta[w] = s;
+      const float l = lse[((size_t)b * Hq + h) * Tq + t];
+      lse2[w] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+    }
+  }
+}
+
+static int make_tmap4(CUtensorMap* m, const void* ptr, int D, int H, int T, int B, long s_head, long s_tok, long s_batch) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)T, (uint64_t)B};
+  uint64_t strides[4] = {0, (uint64_t)s_head * 2, (uint64_t)s_tok * 2, (uint64_t)s_batch * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)FB_T, 1};
+  return encode_tmap(m, ptr, 2, 4, dims, strides, box, 1);
+}
+
+}  // namespace cpb
+
+using namespace cpb;
+
+// o and dout are contiguous [B,Tq,Hq,D]; delta/lse2 are [B,Hq,Tq_pad] with Tq_pad = ceil(Tq/128)*128.
+extern "C" int cpb_flash_bwd_prep(const void* o, const void* dout, const float* lse, float* delta, float* lse2,
+                                  int B, int Tq, int Hq, int D, int Tq_pad, cudaStream_t stream) {
+  const size_t nrow = (size_t)B * Hq * Tq_pad;
+  size_t g = (nrow + 7) / 8;
+  const size_t cap = (size_t)sm_count() * 16;
+  if (g > cap) g = cap;
+  if (D == 64) bwd_prep_kernel<64><<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, lse, delta, lse2, B, Tq, Hq, Tq_pad);
+  else if (D == 128) bwd_prep_kernel<128><<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, lse, delta, lse2, B, Tq, Hq, Tq_pad);
+  else return set_error(CPB_ERR_ARG, "flash_bwd_prep: head_dim %d not in {64,128}", D);
+  return check_launch("flash_bwd_prep");
+}
+
+// q,k,v: strided views (element strides: head, token, batch); dout contiguous [B,Tq,Hq,D].
+// dq: fp32 [B,Tq,Hq,D] (accumulated; caller zeroes).  dk/dv: [B,Tk,Hkv,D] bf16 (written) or fp32 (+=).
+// q_pos: int32 [Tq_pad] (INT_MAX padding) -- required.
+extern "C" int cpb_flash_bwd(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                             const float* delta, float* dq, void* dk, void* dv,
+                             int B, int Tq, int Tk, int Hq, int Hkv, int D, int Tq_pad,
+                             long q_sh, long q_st, long q_sb, long k_sh, long k_st, long k_sb,
+                             float scale, int causal, int k_off, const int* q_pos, int dkv_f32_accumulate,
+                             int* status, cudaStream_t stream) {
+  if (D != 64 && D != 128) return set_error(CPB_ERR_ARG, "flash_bwd: head_dim %d not in {64,128}", D);
+  if (Hq % Hkv) return set_error(CPB_ERR_ARG, "flash_bwd: Hq %% Hkv != 0");
+  if (Tq_pad % FB_T || Tq_pad < Tq) return set_error(CPB_ERR_ARG, "flash_bwd: bad Tq_pad");
+  if (q_pos == nullptr) return set_error(CPB_ERR_ARG, "flash_bwd: q_pos is required");
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_tmap4(&tq, q, D, Hq, Tq, B, q_sh, q_st, q_sb)) != CPB_OK) return rc;
+  if ((rc = make_tmap4(&tk, k, D, Hkv, Tk, B, k_sh, k_st, k_sb)) != CPB_OK) return rc;
+  if ((rc = make_tmap4(&tv, v, D, Hkv, Tk, B, k_sh, k_st, k_sb)) != CPB_OK) return rc;
+  if ((rc = make_tmap4(&tdo, dout, D, Hq, Tq, B, D, (long)Hq * D, (long)Tq * Hq * D)) != CPB_OK) return rc;
+  BwdParams p;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv; p.Tq_pad = Tq_pad; p.causal = causal; p.k_off = k_off;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse2 = lse2; p.delta = delta; p.q_pos = q_pos; p.dq = dq; p.dk = dk; p.dv = dv;
+  p.dkv_f32_accumulate = dkv_f32_accumulate; p.status = status;
+  dim3 grid((Tk + FB_T - 1) / FB_T, Hkv, B);
+  if (D == 64) {
+    static bool cfg = false;
+    if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::TOTAL)); cfg = true; }
+    flash_bwd_kernel<64><<<grid, FB_THREADS, BwdSmem<64>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::TOTAL)); cfg = true; }
+    flash_bwd_kernel<128><<<grid, FB_THREADS, BwdSmem<128>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  }
+  return check_launch("flash_bwd");
+}

@@ -52,6 +52,10 @@ int encode_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, co
                 const uint64_t* strides_bytes, const uint32_t* box, int swizzle128) {
   auto fn = get_encode();
   if (fn == nullptr) return set_error(CPB_ERR_DRIVER, "cuTensorMapEncodeTiled entry point unavailable");
+  // The driver call needs a current context; a thread that has made no runtime call yet (an autograd
+  // worker thread, for instance) has none until the runtime binds the primary context.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(0); ctx_bound = true; }
   if (((uintptr_t)base & 15) != 0) return set_error(CPB_ERR_ARG, "tensor map base %p not 16-byte aligned", base);
   cuuint64_t gdim[5], gstride[5];
   cuuint32_t bdim[5], estride[5];

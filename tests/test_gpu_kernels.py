@@ -177,3 +177,46 @@ def test_flash_fwd_positions_packed():
     want, wlse = R.attention_dense(q.float(), k.float(), v.float(), 0.125, q_pos=pos, causal=True)
     assert_close(out.float(), want, cos=0.999, rel=3e-2, name="out")
     assert_close(lse, wlse, cos=0.99999, rel=1e-3, name="lse")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("B,Tq,Tk,Hq,Hkv,causal", [
+    (1, 128, 128, 1, 1, False), (1, 128, 128, 1, 1, True), (2, 384, 384, 4, 2, True),
+    (1, 200, 328, 2, 1, False), (1, 1024, 1024, 4, 1, True)])
+def test_flash_bwd(D, B, Tq, Tk, Hq, Hkv, causal):
+    from context_parallelism_b200.ops import attention as A, reference as R
+    torch.manual_seed(7)
+    q = torch.randn(B, Tq, Hq, D, device=dev()).bfloat16()
+    k = torch.randn(B, Tk, Hkv, D, device=dev()).bfloat16()
+    v = torch.randn(B, Tk, Hkv, D, device=dev()).bfloat16()
+    do = torch.randn(B, Tq, Hq, D, device=dev()).bfloat16()
+    scale = 1 / math.sqrt(D)
+    out, lse = A.flash_fwd(q, k, v, scale, causal)
+    dq, dk, dv = A.flash_bwd(q, k, v, out, lse, do, scale, causal)
+    check_status()
+    want, wlse = R.attention_dense(q.float(), k.float(), v.float(), scale, causal=causal)
+    wdq, wdk, wdv = R.attention_dense_bwd(q.float(), k.float(), v.float(), want, wlse, do.float(), scale, causal=causal)
+    assert_close(dv.float(), wdv, cos=0.995, rel=5e-2, name="dv")
+    assert_close(dk.float(), wdk, cos=0.995, rel=5e-2, name="dk")
+    assert_close(dq.float(), wdq, cos=0.995, rel=5e-2, name="dq")
+
+
+def test_flash_autograd_positions():
+    from context_parallelism_b200.ops import attention as A
+    from context_parallelism_b200.parallel.shard import local_positions
+    torch.manual_seed(8)
+    B, T, Hq, Hkv, D, N, r = 1, 1024, 4, 2, 64, 4, 2
+    pos = local_positions(T, N, r, True).to(dev())
+    q = torch.randn(B, T // N, Hq, D, device=dev()).bfloat16().requires_grad_()
+    k = torch.randn(B, T, Hkv, D, device=dev()).bfloat16().requires_grad_()
+    v = torch.randn(B, T, Hkv, D, device=dev()).bfloat16().requires_grad_()
+    out, _ = A.flash_attention(q, k, v, None, True, pos.int())
+    do = torch.randn_like(out)
+    out.backward(do)
+    check_status()
+    Q, K, V = (t.detach().float().cpu().requires_grad_() for t in (q, k, v))
+    want, _ = A.flash_attention(Q, K, V, None, True, pos.cpu())
+    want.backward(do.float().cpu())
+    assert_close(out.float().cpu(), want, cos=0.999, name="out")
+    for a, b_, n in ((q, Q, "dq"), (k, K, "dk"), (v, V, "dv")):
+        assert_close(a.grad.float().cpu(), b_.grad, cos=0.995, name=n)
