@@ -62,11 +62,21 @@ def ptr(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0) if t is None else c_void_p(t.data_ptr())
 
 
+LAUNCHES = [0]          # number of kernel launchers invoked (each launches exactly one of our kernels)
+_FN_CACHE = {}
+
+
 def call(name: str, *args) -> None:
     """Invoke ``cpb_<name>`` with already-converted ctypes arguments and raise on error."""
-    fn = getattr(lib(), "cpb_" + name)
-    fn.restype = c_int
-    check(fn(*args), name)
+    fn = _FN_CACHE.get(name)
+    if fn is None:
+        fn = getattr(lib(), "cpb_" + name)
+        fn.restype = c_int
+        _FN_CACHE[name] = fn
+    LAUNCHES[0] += 1
+    rc = fn(*args)
+    if rc != 0:
+        check(rc, name)
 
 
 # --------------------------------------------------------------------------- kernel status words

@@ -247,6 +247,12 @@ class Config:
 
     # ------------------------------------------------------------------ derived
     @property
+    def vocab_padded(self) -> int:
+        """Embedding / lm_head rows: the vocabulary rounded up to a multiple of 64 (the reference pads 50257 to
+        50304 for the same reason, bluscriptCP.cpp:111); padding rows are zero and never enter the softmax."""
+        return (self.vocab_size + 63) // 64 * 64
+
+    @property
     def dp_size(self) -> int:
         return self.world_size // self.cp_size
 

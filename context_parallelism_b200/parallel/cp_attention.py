@@ -1,0 +1,124 @@
+"""Context-parallel attention layer: one entry point for every mode.
+
+``CPAttention(qkv, pos)`` takes the packed, already normalised and rotated projections of the LOCAL
+tokens ``[B, T_local, (Hq + 2·Hkv)·D]`` with their global positions and returns ``[B, T_local, Hq·D]``.
+Modes (``CP_ATTN_MODE``): ``ring`` (HeadTail load-balanced), ``ulysses`` (contiguous shards, head
+all-to-all), ``hybrid`` (Ulysses inside, ring outside).  Transport (``CP_ROTATOR``): ``fused`` uses the
+peer-memory kernels of this package; ``p2p`` / ``alltoall`` / ``allgather`` select the NCCL-only
+baseline built on ``torch.distributed``.  This mirrors the dispatch of
+``ContextParallel::forward_cp`` (context_parallel/ContextParallel.h:405-422,1359-1396) with
+``pre_sharded=true, unshard=false``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config import Config
+from ..ops import attention as A
+from . import shard
+from .mesh import DeviceMesh
+
+
+@dataclass
+class CPContext:
+    cfg: Config
+    mesh: Optional[DeviceMesh] = None
+    cp_group: object = None
+    cp_rank: int = 0
+    cp_size: int = 1
+    ring_group: object = None
+    ring_rank: int = 0
+    ring_size: int = 1
+    ulysses_group: object = None
+    ulysses_rank: int = 0
+    ulysses_size: int = 1
+    dp_rank: int = 0
+    dp_size: int = 1
+    world_group: object = None
+    fused: object = None            # parallel.fused.FusedComm once initialised (CUDA, same node)
+
+    @staticmethod
+    def single(cfg: Config) -> "CPContext":
+        return CPContext(cfg=cfg)
+
+    @staticmethod
+    def from_mesh(cfg: Config, mesh: DeviceMesh) -> "CPContext":
+        c = CPContext(cfg=cfg, mesh=mesh, world_group=None)
+        c.dp_rank, c.dp_size = mesh.coord("dp"), mesh.size("dp")
+        if cfg.attn_mode == "hybrid":
+            c.ring_group, c.ring_rank, c.ring_size = mesh.group("ring"), mesh.coord("ring"), mesh.size("ring")
+            c.ulysses_group, c.ulysses_rank, c.ulysses_size = mesh.group("ulysses"), mesh.coord("ulysses"), mesh.size("ulysses")
+            c.cp_size = c.ring_size * c.ulysses_size
+            c.cp_rank = c.ring_rank * c.ulysses_size + c.ulysses_rank
+        else:
+            c.cp_group, c.cp_rank, c.cp_size = mesh.group("cp"), mesh.coord("cp"), mesh.size("cp")
+            if cfg.attn_mode == "ring":
+                c.ring_group, c.ring_rank, c.ring_size = c.cp_group, c.cp_rank, c.cp_size
+            else:
+                c.ulysses_group, c.ulysses_rank, c.ulysses_size = c.cp_group, c.cp_rank, c.cp_size
+        return c
+
+    # ------------------------------------------------------------------ sharding of a batch
+    def local_positions(self, T: int) -> torch.Tensor:
+        cfg = self.cfg
+        if self.cp_size == 1:
+            return torch.arange(T)
+        if cfg.attn_mode == "hybrid":
+            return shard.hybrid_local_positions(T, self.ring_size, self.ring_rank, self.ulysses_size, self.ulysses_rank)
+        return shard.local_positions(T, self.cp_size, self.cp_rank, cfg.attn_mode == "ring")
+
+    def ring_positions(self, T: int) -> List[torch.Tensor]:
+        """Position vectors of every ring rank's block (after the Ulysses combine in hybrid mode)."""
+        return [shard.local_positions(T, self.ring_size, s, True) for s in range(self.ring_size)]
+
+
+class CPAttention:
+    def __init__(self, cfg: Config, ctx: CPContext):
+        self.cfg, self.ctx = cfg, ctx
+        self.scale = cfg.head_dim ** -0.5
+        self._pos_cache = {}
+
+    def _ring_pos(self, T: int, device):
+        key = (T, str(device))
+        v = self._pos_cache.get(key)
+        if v is None:
+            allp = self.ctx.ring_positions(T)
+            v = (allp, allp[self.ctx.ring_rank].to(device))
+            self._pos_cache[key] = v
+        return v
+
+    def __call__(self, qkv: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        cfg, ctx = self.cfg, self.ctx
+        B, Tl = qkv.shape[:2]
+        Hq, Hkv, D = cfg.n_head, cfg.n_kv_head, cfg.head_dim
+        x = qkv.view(B, Tl, Hq + 2 * Hkv, D)
+        q, k, v = x[:, :, :Hq], x[:, :, Hq:Hq + Hkv], x[:, :, Hq + Hkv:]
+        mode = cfg.attn_mode if ctx.cp_size > 1 else "single"
+        fused = ctx.fused is not None and cfg.rotator == "fused" and qkv.is_cuda
+        if mode == "single":
+            o, _ = A.flash_attention(q, k, v, self.scale, True)
+        elif mode == "ring":
+            T = Tl * ctx.ring_size
+            allp, mypos = self._ring_pos(T, qkv.device)
+            if fused:
+                o = ctx.fused.ring_attention(q, k, v, mypos, T, self.scale)
+            else:
+                from .ring import ring_attention
+                kind = "p2p" if cfg.rotator == "fused" else cfg.rotator
+                o, _ = ring_attention(q, k, v, mypos, allp, ctx.ring_group, kind, self.scale, not cfg.recompute_k and False)
+        elif mode == "ulysses":
+            if fused:
+                o = ctx.fused.ulysses_attention(q, k, v, self.scale)
+            else:
+                from .ulysses import ulysses_attention
+                o = ulysses_attention(q, k, v, ctx.ulysses_group, self.scale)
+        elif mode == "hybrid":
+            from .hybrid import hybrid_attention
+            o = hybrid_attention(q, k, v, ctx, self, fused)
+        else:
+            raise ValueError(mode)
+        return o.reshape(B, Tl, Hq * D)

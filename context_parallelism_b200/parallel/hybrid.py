@@ -1,0 +1,35 @@
+"""Hybrid (USP) attention: Ulysses all-to-all inside, ring outside.
+
+The Ulysses combine over the inner group turns ``[B, T/(R·U), H, D]`` into ``[B, T/R, H/U, D]`` — the whole
+HeadTail ring block of this ring rank with a slice of the heads — then ring attention runs over the
+outer group and the result is partitioned back (context_parallel/ContextParallel.h:1359-1396,
+context_parallel/HybridUlyssesBackward.h:42-81).  Requires ``q_heads % U == 0`` and ``kv_heads % U == 0``.
+"""
+from __future__ import annotations
+
+import torch
+
+from .ulysses import head_to_seq, seq_to_head
+
+
+def hybrid_attention(q, k, v, ctx, attn, fused: bool):
+    U, R = ctx.ulysses_size, ctx.ring_size
+    if q.shape[2] % U or k.shape[2] % U:
+        raise ValueError("hybrid: q_heads and kv_heads must be multiples of the Ulysses degree")
+    if U > 1:
+        q, k, v = (seq_to_head(t, ctx.ulysses_group) for t in (q, k, v))
+    T = q.shape[1] * R
+    if R > 1:
+        allp, mypos = attn._ring_pos(T, q.device)
+        if fused and ctx.fused.supports_ring_group():
+            o = ctx.fused.ring_attention(q, k, v, mypos, T, attn.scale)
+        else:
+            from .ring import ring_attention
+            kind = "p2p" if attn.cfg.rotator == "fused" else attn.cfg.rotator
+            o, _ = ring_attention(q, k, v, mypos, allp, ctx.ring_group, kind, attn.scale, False)
+    else:
+        from ..ops import attention as A
+        o, _ = A.flash_attention(q, k, v, attn.scale, True)
+    if U > 1:
+        o = head_to_seq(o, ctx.ulysses_group)
+    return o

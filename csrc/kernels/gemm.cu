@@ -307,7 +307,9 @@ extern "C" int cpb_gemm_bf16(const void* A, const void* B, void* C, void* aux, c
                              int M, int N, int K, int lda, int ldb, int ldc, int ld_aux,
                              int a_mn, int b_mn, int epi, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return set_error(CPB_ERR_ARG, "gemm: empty problem %dx%dx%d", M, N, K);
-  if ((K % 8) || (N % 8) || (lda % 8) || (ldb % 8)) return set_error(CPB_ERR_ARG, "gemm: K,N,lda,ldb must be multiples of 8 (got K=%d N=%d lda=%d ldb=%d)", K, N, lda, ldb);
+  // the contiguous dimension of every operand and every row stride must be a multiple of 8 elements (16 bytes)
+  if ((N % 8) || (lda % 8) || (ldb % 8)) return set_error(CPB_ERR_ARG, "gemm: N,lda,ldb must be multiples of 8 (got N=%d lda=%d ldb=%d)", N, lda, ldb);
+  if ((!a_mn || !b_mn) && (K % 8)) return set_error(CPB_ERR_ARG, "gemm: K=%d must be a multiple of 8 for a K-major operand", K);
   if (a_mn && (M % 8)) return set_error(CPB_ERR_ARG, "gemm: M must be a multiple of 8 when A is M-major");
   if (epi == EPI_BF16_SWIGLU && (a_mn || b_mn)) return set_error(CPB_ERR_ARG, "gemm: swiglu epilogue needs K-major operands");
   const int BN = (epi == EPI_BF16_SWIGLU || N > 128) ? 256 : 128;
