@@ -25,17 +25,20 @@ from .utils.lr import cosine_lr, rewarmup_lr
 
 
 class TrainEngine:
-    def __init__(self, cfg: Config, device: Optional[torch.device] = None, mesh: Optional[DeviceMesh] = None):
+    def __init__(self, cfg: Config, device: Optional[torch.device] = None, mesh: Optional[DeviceMesh] = None,
+                 standalone: bool = False):
+        """``standalone=True`` builds a single-process engine (world size 1) even inside a distributed job; the
+        parity tests use it for the unsharded reference run."""
         cfg.validate()
         self.cfg = cfg
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.device = device
-        self.rank = dist.get_rank() if dist.is_initialized() else 0
-        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if (dist.is_initialized() and not standalone) else 0
+        self.world = dist.get_world_size() if (dist.is_initialized() and not standalone) else 1
         if cfg.world_size != self.world:
             raise ValueError(f"config world_size={cfg.world_size} but the job has {self.world} ranks")
-        self.mesh = mesh or DeviceMesh.for_config(cfg, self.rank, self.world)
+        self.mesh = mesh or DeviceMesh.for_config(cfg, self.rank, self.world, create_groups=not standalone)
         self.cp = CPContext.from_mesh(cfg, self.mesh)
         if device.type == "cuda" and self.cp.cp_size > 1 and cfg.rotator == "fused":
             from .parallel.fused import FusedComm

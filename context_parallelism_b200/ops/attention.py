@@ -34,11 +34,15 @@ def _ok_layout(t: torch.Tensor) -> bool:
 def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, causal: bool = True,
               q_pos: Optional[torch.Tensor] = None, k_off: int = 0,
               ready: Optional[torch.Tensor] = None, ready_epoch: int = 0, block_rows: int = 0,
-              out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None
-              ) -> Tuple[torch.Tensor, torch.Tensor]:
+              out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+              segs: Optional[torch.Tensor] = None, n_segs: int = 0, n_copy: int = 0,
+              o_scatter: Optional[tuple] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Forward only (no autograd).  ``q_pos`` is int32 ``[Tq]``.  ``ready``/``ready_epoch``/``block_rows``
     make the kernel wait, before it first touches K/V rows of block ``c``, until ``ready[c] >= ready_epoch``
-    (used by the fused ring while remote blocks are still arriving)."""
+    (used by the fused ring while remote blocks are still arriving).  ``segs``/``n_segs``/``n_copy`` add copy
+    CTAs that pull the listed K/V segments from peers and bump ``ready``.  ``o_scatter = (peer_table, byte_off,
+    rows_per_peer, head_off, heads_total)`` makes the epilogue store rows into their token owners' arenas
+    (then ``out`` is not written)."""
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     if not _ok_layout(q):
@@ -50,7 +54,8 @@ def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, c
         if v.stride() != k.stride():
             k = k.contiguous()
     if out is None:
-        out = torch.empty((B, Tq, Hq, D), dtype=torch.bfloat16, device=q.device)
+        out = (torch.empty((B, Tq, Hq, D), dtype=torch.bfloat16, device=q.device) if o_scatter is None
+               else torch.empty((1,), dtype=torch.bfloat16, device=q.device))
     if lse is None:
         lse = torch.empty((B, Hq, Tq), dtype=torch.float32, device=q.device)
     if q_pos is not None:
@@ -61,7 +66,10 @@ def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, c
             nv.i(B), nv.i(Tq), nv.i(Tk), nv.i(Hq), nv.i(Hkv), nv.i(D),
             nv.l(qs[0]), nv.l(qs[1]), nv.l(qs[2]), nv.l(ks[0]), nv.l(ks[1]), nv.l(ks[2]),
             nv.f(scale), nv.i(causal), nv.i(k_off), nv.ptr(q_pos), nv.ptr(ready), nv.i(ready_epoch),
-            nv.i(block_rows), st.ptr(), nv.stream_ptr(q.device))
+            nv.i(block_rows), nv.ptr(segs), nv.i(n_segs), nv.i(n_copy),
+            nv.ptr(o_scatter[0] if o_scatter else None), nv.l(o_scatter[1] if o_scatter else 0),
+            nv.i(o_scatter[2] if o_scatter else 0), nv.i(o_scatter[3] if o_scatter else 0),
+            nv.i(o_scatter[4] if o_scatter else 0), st.ptr(), nv.stream_ptr(q.device))
     return out, lse
 
 

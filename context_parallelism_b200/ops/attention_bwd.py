@@ -32,9 +32,32 @@ def flash_bwd_prep(o: torch.Tensor, do: torch.Tensor, lse: torch.Tensor):
     return delta, lse2
 
 
-def flash_bwd_core(q, k, v, do, lse2, delta, qpos_pad, scale, causal, k_off, dq_f32, dk, dv, dkv_accumulate):
+def flash_bwd_delta(o: torch.Tensor, do: torch.Tensor) -> torch.Tensor:
+    """Only ``delta = rowsum(dO∘O)`` ``[B,Hq,Tq_pad]`` (computed where the tokens live)."""
+    B, Tq, Hq, D = o.shape
+    tq_pad = (Tq + 127) // 128 * 128
+    delta = torch.empty((B, Hq, tq_pad), dtype=torch.float32, device=o.device)
+    nv.call("flash_bwd_prep", nv.ptr(o), nv.ptr(do), nv.ptr(None), nv.ptr(delta), nv.ptr(None),
+            nv.i(B), nv.i(Tq), nv.i(Hq), nv.i(D), nv.i(tq_pad), nv.stream_ptr(o.device))
+    return delta
+
+
+def flash_bwd_lse2(lse: torch.Tensor, D: int) -> torch.Tensor:
+    """Only ``lse·log2(e)`` padded ``[B,Hq,Tq_pad]``."""
+    B, Hq, Tq = lse.shape
+    tq_pad = (Tq + 127) // 128 * 128
+    lse2 = torch.empty((B, Hq, tq_pad), dtype=torch.float32, device=lse.device)
+    nv.call("flash_bwd_prep", nv.ptr(None), nv.ptr(None), nv.ptr(lse), nv.ptr(None), nv.ptr(lse2),
+            nv.i(B), nv.i(Tq), nv.i(Hq), nv.i(D), nv.i(tq_pad), nv.stream_ptr(lse.device))
+    return lse2
+
+
+def flash_bwd_core(q, k, v, do, lse2, delta, qpos_pad, scale, causal, k_off, dq_f32, dk, dv, dkv_accumulate,
+                   route=None):
     """One launch of the backward kernel: ``dq_f32`` (fp32) is accumulated with atomics; ``dk``/``dv`` are
-    written as bf16, or accumulated in fp32 when ``dkv_accumulate``."""
+    written as bf16, or accumulated in fp32 when ``dkv_accumulate``.  ``route = (route_k, route_v, rows, tl)``
+    (int64 device tables of per-chunk owner addresses) makes the epilogue add each dK/dV tile into its owner's
+    fp32 accumulator over NVLink instead."""
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     st = nv.status_for(q.device)
@@ -43,8 +66,9 @@ def flash_bwd_core(q, k, v, do, lse2, delta, qpos_pad, scale, causal, k_off, dq_
     nv.call("flash_bwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(do), nv.ptr(lse2), nv.ptr(delta), nv.ptr(dq_f32),
             nv.ptr(dk), nv.ptr(dv), nv.i(B), nv.i(Tq), nv.i(Tk), nv.i(Hq), nv.i(Hkv), nv.i(D), nv.i(lse2.shape[-1]),
             nv.l(qs[0]), nv.l(qs[1]), nv.l(qs[2]), nv.l(ks[0]), nv.l(ks[1]), nv.l(ks[2]),
-            nv.f(scale), nv.i(causal), nv.i(k_off), nv.ptr(qpos_pad), nv.i(dkv_accumulate), st.ptr(),
-            nv.stream_ptr(q.device))
+            nv.f(scale), nv.i(causal), nv.i(k_off), nv.ptr(qpos_pad), nv.i(2 if route is not None else int(dkv_accumulate)),
+            nv.ptr(route[0] if route else None), nv.ptr(route[1] if route else None),
+            nv.i(route[2] if route else 0), nv.i(route[3] if route else 0), st.ptr(), nv.stream_ptr(q.device))
 
 
 def cast_to_bf16(x_f32: torch.Tensor, scale: float = 1.0) -> torch.Tensor:

@@ -79,7 +79,7 @@ class _NormFn(torch.autograd.Function):
             r2, xnew = None, x2
         nv.call("norm_fwd", nv.ptr(x2), nv.ptr(r2), nv.ptr(w), nv.ptr(b), nv.ptr(xnew), nv.ptr(y), nv.ptr(stats),
                 nv.i(rows), nv.i(d), nv.f(eps), nv.i(layer), nv.stream_ptr(x.device))
-        ctx.save_for_backward(xnew, stats, w)
+        ctx.save_for_backward(xnew, stats)
         ctx.w, ctx.b, ctx.layer, ctx.has_res = w, b, layer, res is not None
         ctx.shape = x.shape
         ctx.set_materialize_grads(False)
@@ -87,7 +87,8 @@ class _NormFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, dxnew):
-        xnew, stats, w = ctx.saved_tensors
+        xnew, stats = ctx.saved_tensors
+        w = ctx.w
         d = xnew.shape[-1]
         if dy is None:
             dy = torch.zeros(ctx.shape, dtype=xnew.dtype, device=xnew.device)

@@ -98,7 +98,10 @@ class _LinearFn(torch.autograd.Function):
     def forward(ctx, x, w, b):
         x2 = x.reshape(-1, x.shape[-1])
         y = gemm(x2, w, bias=b)
-        ctx.save_for_backward(x2, w)
+        # The parameter objects are kept as plain attributes: under activation recomputation the tensors handed
+        # back by ``saved_tensors`` are fresh objects without ``main_grad`` / ``_grad_ready``.
+        ctx.save_for_backward(x2)
+        ctx.weight = w
         ctx.has_bias = b is not None
         ctx.bias = b
         ctx.xshape = x.shape
@@ -106,7 +109,7 @@ class _LinearFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x2, w = ctx.saved_tensors
+        (x2,), w = ctx.saved_tensors, ctx.weight
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
@@ -135,14 +138,15 @@ class _LinearSwiGLUFn(torch.autograd.Function):
         Fh = w.shape[0] // 2
         gu = torch.empty((x2.shape[0], 2 * Fh), dtype=torch.bfloat16, device=x.device)
         act = gemm(x2, w, epi=EPI_BF16_SWIGLU, aux=gu)
-        ctx.save_for_backward(x2, w, gu)
+        ctx.save_for_backward(x2, gu)
+        ctx.weight = w
         ctx.xshape = x.shape
         return act.view(*x.shape[:-1], Fh)
 
     @staticmethod
     def backward(ctx, dact):
         from .elementwise import swiglu_bwd
-        x2, w, gu = ctx.saved_tensors
+        (x2, gu), w = ctx.saved_tensors, ctx.weight
         d2 = dact.reshape(-1, dact.shape[-1])
         if not d2.is_contiguous():
             d2 = d2.contiguous()
@@ -165,7 +169,8 @@ class _LinearGELUFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         pre = torch.empty((x2.shape[0], w.shape[0]), dtype=torch.bfloat16, device=x.device)
         act = gemm(x2, w, bias=b, epi=EPI_BF16_GELU, aux=pre)
-        ctx.save_for_backward(x2, w, pre)
+        ctx.save_for_backward(x2, pre)
+        ctx.weight = w
         ctx.bias = b
         ctx.xshape = x.shape
         return act.view(*x.shape[:-1], w.shape[0])
@@ -173,7 +178,7 @@ class _LinearGELUFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dact):
         from .elementwise import bias_grad_into, gelu_bwd
-        x2, w, pre = ctx.saved_tensors
+        (x2, pre), w = ctx.saved_tensors, ctx.weight
         d2 = dact.reshape(-1, dact.shape[-1])
         if not d2.is_contiguous():
             d2 = d2.contiguous()

@@ -46,7 +46,7 @@ def headtail_unloadbalance(x: torch.Tensor, n: int, dim: int = 1) -> torch.Tenso
     return gather_seq(x, shard.headtail_inverse_perm(x.shape[dim], n), dim)
 
 
-def kv_pack(k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+def kv_pack(k: torch.Tensor, v: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
     """Strided ``[B,T,H,D]`` K and V views → one contiguous ``[2,B,T,H,D]`` buffer (the message of one
     ring hop)."""
     B, T, H, D = k.shape
@@ -55,7 +55,8 @@ def kv_pack(k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     ok = lambda t: t.stride(3) == 1 and t.stride(2) == D and t.stride(0) == T * t.stride(1)
     if not (ok(k) and ok(v)):
         k, v = k.contiguous(), v.contiguous()
-    out = torch.empty((2, B, T, H, D), dtype=k.dtype, device=k.device)
+    if out is None:
+        out = torch.empty((2, B, T, H, D), dtype=k.dtype, device=k.device)
     nv.call("kv_pack", nv.ptr(k), nv.ptr(v), nv.ptr(out), nv.l(B * T), nv.i(H * D), nv.l(k.stride(1)), nv.l(v.stride(1)),
             nv.stream_ptr(k.device))
     return out

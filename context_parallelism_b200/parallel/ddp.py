@@ -122,6 +122,12 @@ class GradReducer:
         for b in range(len(self.buckets)):
             if not self._launched[b]:
                 self._launch(b)
+        if self.fused is not None:
+            if self.stream is not None:
+                with torch.cuda.stream(self.stream):
+                    self.fused.allreduce_finish()
+            else:
+                self.fused.allreduce_finish()
         if self.stream is not None:
             torch.cuda.current_stream(self.flat.device).wait_stream(self.stream)
 

@@ -38,6 +38,13 @@ struct BwdParams {
   float* dq;                // [B,Tq,Hq,D] fp32, accumulated with red.add
   void* dk; void* dv;       // [B,Tk,Hkv,D] bf16 (store) or fp32 (accumulate)
   int dkv_f32_accumulate;
+  // fused ring (dkv_f32_accumulate == 2): K/V row kidx belongs to chunk c = kidx / route_rows, owned by some
+  // rank; route_k[c] / route_v[c] are the addresses (peer-mapped) of that owner's fp32 accumulators at the
+  // chunk's first local row for batch 0, whose layout is [B, route_tl, Hkv, D].  The epilogue adds the tile
+  // with red.global.add over NVLink.
+  const uint64_t* route_k;
+  const uint64_t* route_v;
+  int route_rows, route_tl;
   int* status;
 };
 
@@ -278,7 +285,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tmem_ld32(t_lane + col + c, v);
             tmem_wait_ld();
             if (k_valid) {
-              if (p.dkv_f32_accumulate) {
+              if (p.dkv_f32_accumulate == 2) {
+                const int ch = kidx / p.route_rows, lrow = kidx % p.route_rows;
+                float* dst = (float*)(which ? p.route_v[ch] : p.route_k[ch]) +
+                             (((size_t)b * p.route_tl + lrow) * p.Hkv + hkv) * D + c;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  red_add_v4(dst + j, __uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+              } else if (p.dkv_f32_accumulate) {
                 float* dst = (float*)base + off + c;
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
@@ -350,20 +364,22 @@ __global__ void bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
     const int h = (int)((w / Tq_pad) % Hq);
     const int b = (int)(w / ((size_t)Tq_pad * Hq));
     if (t >= Tq) {
-      if (lane == 0) { delta[w] = 0.f; lse2[w] = INFINITY; }
+      if (lane == 0) { if (delta) delta[w] = 0.f; if (lse2) lse2[w] = INFINITY; }
       continue;
     }
-    const size_t off = (((size_t)b * Tq + t) * Hq + h) * D;
-    float s = 0.f;
+    if (delta) {
+      const size_t off = (((size_t)b * Tq + t) * Hq + h) * D;
+      float s = 0.f;
 #pragma unroll
-    for (int e = lane * 2; e < D; e += 64) {
-      const uint32_t a = *(const uint32_t*)(o + off + e), g = *(const uint32_t*)(dout + off + e);
-      s += bf16_lo(a) * bf16_lo(g) + bf16_hi(a) * bf16_hi(g);
+      for (int e = lane * 2; e < D; e += 64) {
+        const uint32_t a = *(const uint32_t*)(o + off + e), g = *(const uint32_t*)(dout + off + e);
+        s += bf16_lo(a) * bf16_lo(g) + bf16_hi(a) * bf16_hi(g);
+      }
+#pragma unroll
+      for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+      if (lane == 0) delta[w] = s;
     }
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-    if (lane == 0) {
-      delta[w] = s;
+    if (lse2 && lane == 0) {
       const float l = lse[((size_t)b * Hq + h) * Tq + t];
       lse2[w] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
     }
@@ -382,6 +398,8 @@ static int make_tmap4(CUtensorMap* m, const void* ptr, int D, int H, int T, int 
 using namespace cpb;
 
 // o and dout are contiguous [B,Tq,Hq,D]; delta/lse2 are [B,Hq,Tq_pad] with Tq_pad = ceil(Tq/128)*128.
+// Either output may be null (then its inputs are not read): the Ulysses backward computes delta where the
+// tokens live and lse2 where the heads live.
 extern "C" int cpb_flash_bwd_prep(const void* o, const void* dout, const float* lse, float* delta, float* lse2,
                                   int B, int Tq, int Hq, int D, int Tq_pad, cudaStream_t stream) {
   const size_t nrow = (size_t)B * Hq * Tq_pad;
@@ -402,6 +420,7 @@ extern "C" int cpb_flash_bwd(const void* q, const void* k, const void* v, const 
                              int B, int Tq, int Tk, int Hq, int Hkv, int D, int Tq_pad,
                              long q_sh, long q_st, long q_sb, long k_sh, long k_st, long k_sb,
                              float scale, int causal, int k_off, const int* q_pos, int dkv_f32_accumulate,
+                             const uint64_t* route_k, const uint64_t* route_v, int route_rows, int route_tl,
                              int* status, cudaStream_t stream) {
   if (D != 64 && D != 128) return set_error(CPB_ERR_ARG, "flash_bwd: head_dim %d not in {64,128}", D);
   if (Hq % Hkv) return set_error(CPB_ERR_ARG, "flash_bwd: Hq %% Hkv != 0");
@@ -418,6 +437,9 @@ extern "C" int cpb_flash_bwd(const void* q, const void* k, const void* v, const 
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.lse2 = lse2; p.delta = delta; p.q_pos = q_pos; p.dq = dq; p.dk = dk; p.dv = dv;
   p.dkv_f32_accumulate = dkv_f32_accumulate; p.status = status;
+  p.route_k = route_k; p.route_v = route_v; p.route_rows = route_rows; p.route_tl = route_tl;
+  if (dkv_f32_accumulate == 2 && (route_k == nullptr || route_v == nullptr || route_rows <= 0))
+    return set_error(CPB_ERR_ARG, "flash_bwd: routed dK/dV needs route tables");
   dim3 grid((Tk + FB_T - 1) / FB_T, Hkv, B);
   if (D == 64) {
     static bool cfg = false;

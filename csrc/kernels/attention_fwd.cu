@@ -19,6 +19,7 @@
 // gqa_fused_rope_v2 (context_parallel/GQA_fused_fwd_sm103_cp.cu:117-281).
 #include "common.cuh"
 #include "host_utils.h"
+#include "ring_copy.cuh"
 
 namespace cpb {
 
@@ -37,9 +38,21 @@ struct FwdParams {
   float* lse;                // [B,Hq,Tq]
   // fused-ring readiness flags: K/V rows [c*block_rows, (c+1)*block_rows) may be read once
   // ready[c] >= ready_epoch.  null -> everything is ready.
-  const int* ready;
+  int* ready;
   int ready_epoch;
   int block_rows;
+  // fused ring: the first n_copy CTAs (blockIdx.x < n_copy, y = z = 0) pull the K/V blocks listed in segs into
+  // the local position-ordered buffer and bump ready[]; the compute CTAs start on the chunk that holds
+  // their own diagonal (local data) and wrap around while remote chunks land.
+  const CopySeg* segs;
+  int n_segs;
+  int n_copy;
+  // Ulysses: when o_peers != null the epilogue stores each output row straight into the arena of the rank
+  // that owns the token: row qi -> peer qi / o_rows_per_peer, local row qi % o_rows_per_peer, layout
+  // [B, o_rows_per_peer, o_heads_total, D] at byte offset o_off, head slot o_head_off + hq.
+  const uint64_t* o_peers;
+  long o_off;
+  int o_rows_per_peer, o_head_off, o_heads_total;
   int* status;
 };
 
@@ -72,6 +85,11 @@ __global__ void __launch_bounds__(FA_THREADS, (D == 64 ? 2 : 1))
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, FwdParams p) {
   using L = FwdSmem<D>;
+  if (p.n_copy > 0 && blockIdx.x < (unsigned)p.n_copy) {
+    if (blockIdx.y == 0 && blockIdx.z == 0) ring_copy_cta(p.segs, p.n_segs, p.n_copy, blockIdx.x, p.ready);
+    return;
+  }
+  const int bx = (int)blockIdx.x - p.n_copy;
   constexpr int DH = D / 64;                // 64-wide halves of the head dimension
   constexpr uint32_t TMEM_COLS = 256;
   constexpr uint32_t O_COL = 128;
@@ -91,9 +109,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.Hq / p.Hkv;
   const int num_q_tiles = (p.Tq + FA_BQ - 1) / FA_BQ;
-  const int qt = num_q_tiles - 1 - (int)(blockIdx.x / G);     // heaviest tiles first
+  const int qt = num_q_tiles - 1 - bx / G;                   // heaviest tiles first
   const int hkv = blockIdx.y;
-  const int hq = hkv * G + (int)(blockIdx.x % G);
+  const int hq = hkv * G + bx % G;
   const int b = blockIdx.z;
   const int q0 = qt * FA_BQ;
 
@@ -105,6 +123,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (p.causal) {
     const int last_idx = qpos_max - p.k_off;                  // last visible K index
     n_kv = last_idx < 0 ? 0 : min(n_kv, last_idx / FA_BK + 1);
+  }
+  // Order of the K/V sweep: tile (j + j_start) % n_kv.  With readiness flags the sweep starts at the chunk
+  // that contains this tile's own positions (resident locally), so remote chunks have time to arrive.
+  int j_start = 0;
+  if (p.ready != nullptr && n_kv > 0 && (p.block_rows % FA_BK) == 0) {
+    const int c = max(qpos_min - p.k_off, 0) / p.block_rows;
+    j_start = min(c * (p.block_rows / FA_BK), n_kv - 1);
   }
 
   if (threadIdx.x == 0) {
@@ -134,11 +159,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, p.status, 500)) break;
-        const int k0 = j * FA_BK;
+        const int jj = j + j_start;
+        const int k0 = (jj >= n_kv ? jj - n_kv : jj) * FA_BK;
         if (p.ready != nullptr) {
           // a tile may straddle two blocks when block_rows is not a multiple of the tile
           const int blk_hi = min(k0 + FA_BK, p.Tk) - 1;
-          for (int c = max(ready_block + 1, k0 / p.block_rows); c <= blk_hi / p.block_rows; ++c) {
+          for (int c = k0 / p.block_rows; c <= blk_hi / p.block_rows; ++c) {
+            if (c == ready_block) continue;
             if (!wait_flag_ge(p.ready + c, p.ready_epoch, abort_flag, p.status, 501)) break;
             ready_block = c;
           }
@@ -213,7 +240,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { alive = false; break; }
       tc_fence_after();
-      const int k0 = j * FA_BK;
+      const int jj = j + j_start;
+      const int k0 = (jj >= n_kv ? jj - n_kv : jj) * FA_BK;
       const bool need_mask = (k0 + FA_BK > p.Tk) || (p.causal && (k0 + FA_BK - 1 + p.k_off > qpos_min));
       const int kmax_causal = p.causal ? (my_qpos - p.k_off) : 0x7fffffff;   // last visible index
       const int kmax = min(kmax_causal, p.Tk - 1) - k0;                       // last visible column of this tile
@@ -285,6 +313,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_after();
         const float inv_l = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* orow = p.O + (((size_t)b * p.Tq + (row_valid ? qi : 0)) * p.Hq + hq) * D;
+        if (p.o_peers != nullptr && row_valid) {
+          const int peer = qi / p.o_rows_per_peer, lrow = qi % p.o_rows_per_peer;
+          orow = (__nv_bfloat16*)(p.o_peers[peer] + p.o_off) +
+                 (((size_t)b * p.o_rows_per_peer + lrow) * p.o_heads_total + p.o_head_off + hq) * D;
+        }
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
           uint32_t v[32];
@@ -308,6 +341,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     } else if (n_kv == 0 && row_valid) {
       // no visible key at all: zero output, LSE = -inf
       __nv_bfloat16* orow = p.O + (((size_t)b * p.Tq + qi) * p.Hq + hq) * D;
+      if (p.o_peers != nullptr) {
+        const int peer = qi / p.o_rows_per_peer, lrow = qi % p.o_rows_per_peer;
+        orow = (__nv_bfloat16*)(p.o_peers[peer] + p.o_off) +
+               (((size_t)b * p.o_rows_per_peer + lrow) * p.o_heads_total + p.o_head_off + hq) * D;
+      }
 #pragma unroll
       for (int c = 0; c < D; c += 8) *(uint4*)(orow + c) = make_uint4(0, 0, 0, 0);
       p.lse[((size_t)b * p.Hq + hq) * p.Tq + qi] = -INFINITY;
@@ -336,7 +374,10 @@ extern "C" int cpb_flash_fwd(const void* q, const void* k, const void* v, void* 
                              int B, int Tq, int Tk, int Hq, int Hkv, int D,
                              long q_sh, long q_st, long q_sb, long k_sh, long k_st, long k_sb,
                              float scale, int causal, int k_off, const int* q_pos,
-                             const int* ready, int ready_epoch, int block_rows, int* status, cudaStream_t stream) {
+                             int* ready, int ready_epoch, int block_rows,
+                             const void* segs, int n_segs, int n_copy,
+                             const uint64_t* o_peers, long o_off, int o_rows_per_peer, int o_head_off, int o_heads_total,
+                             int* status, cudaStream_t stream) {
   if (D != 64 && D != 128) return set_error(CPB_ERR_ARG, "flash_fwd: head_dim %d not in {64,128}", D);
   if (Hq % Hkv) return set_error(CPB_ERR_ARG, "flash_fwd: Hq %% Hkv != 0");
   if (B <= 0 || Tq <= 0 || Tk <= 0) return set_error(CPB_ERR_ARG, "flash_fwd: empty problem");
@@ -351,8 +392,12 @@ extern "C" int cpb_flash_fwd(const void* q, const void* k, const void* v, void* 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.q_pos = q_pos; p.O = (__nv_bfloat16*)o; p.lse = lse;
   p.ready = ready; p.ready_epoch = ready_epoch; p.block_rows = block_rows; p.status = status;
+  p.segs = (const CopySeg*)segs; p.n_segs = n_segs; p.n_copy = (segs != nullptr && n_segs > 0) ? n_copy : 0;
+  p.o_peers = o_peers; p.o_off = o_off; p.o_rows_per_peer = o_rows_per_peer; p.o_head_off = o_head_off;
+  p.o_heads_total = o_heads_total;
+  if (p.n_copy > 0 && ready == nullptr) return set_error(CPB_ERR_ARG, "flash_fwd: copy CTAs need ready flags");
   const int G = Hq / Hkv;
-  dim3 grid(((Tq + FA_BQ - 1) / FA_BQ) * G, Hkv, B);
+  dim3 grid(p.n_copy + ((Tq + FA_BQ - 1) / FA_BQ) * G, Hkv, B);
   if (D == 64) {
     static bool cfg = false;
     if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::TOTAL)); cfg = true; }

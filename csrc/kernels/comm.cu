@@ -1,0 +1,274 @@
+// Peer-memory communication kernels (NVLink / NVSwitch, plain loads and stores on peer-mapped
+// addresses; no TMA multicast, no multimem): cross-rank barrier on flag pads, K/V block gather for
+// the ring, Ulysses sequence<->head exchanges, and the two-shot gradient all-reduce with the bf16
+// cast/scale folded in.
+//
+// Every rank owns an arena of identical layout (csrc/runtime/symm.cpp); `peers[r]` is the address of
+// rank r's arena in this process.  Flags are int32 epochs that only grow, so they are never reset.
+// Every wait is bounded and reports into the status word instead of hanging.
+//
+// These replace the NCCL call sites of the reference: ring send/recv (context_parallel/RingRotator.h:
+// 150-152), the Ulysses all-to-all (context_parallel/UlyssesAttention.h:61,91), and the parameter
+// gradient all-reduce (Scripts/Blutrain/gpt2_cp_test.cpp:1594-1600, bluscriptCP.cpp:1003-1012,1716).
+#include "common.cuh"
+#include "host_utils.h"
+#include "ring_copy.cuh"
+
+namespace cpb {
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// ---------------------------------------------------------------------------- barrier
+// Thread r (< world) publishes `epoch` into slot [my_rank] of rank r's flag row, then waits until rank
+// r's epoch shows up in the local row.  Launched on the compute stream it orders everything before it
+// on every rank before everything after it on every rank.
+__global__ void barrier_kernel(const uint64_t* __restrict__ peers, long flag_off, int world, int my_rank, int epoch,
+                               long spin_limit, int* status) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  int* remote = (int*)(peers[r] + flag_off) + my_rank;
+  st_release_sys(remote, epoch);
+  const int* local = (const int*)(peers[my_rank] + flag_off) + r;
+  for (long it = 0; it < spin_limit; ++it) {
+    if (ld_acquire_sys(local) >= epoch) return;
+    __nanosleep(100);
+  }
+  report(status, ST_TIMEOUT_FLAG, 2000, r);
+}
+
+// ---------------------------------------------------------------------------- ring K/V gather
+__global__ void ring_gather_kernel(const CopySeg* __restrict__ segs, int n_segs, int* ready) {
+  ring_copy_cta(segs, n_segs, gridDim.x, blockIdx.x, ready);
+}
+
+// ---------------------------------------------------------------------------- Ulysses exchanges
+struct A2APart {
+  const __nv_bfloat16* src;   // local [B, Tl, *, D] view: element (b,t,h,:) at src + (b*Tl + t)*src_tok_stride + h*D
+  long src_tok_stride;
+  int n_local;                // heads of this part every peer receives
+  int rep;                    // source head = (peer*n_local + j) / rep  (rep > 1: KV heads replicated)
+  int dst_head_off;           // first head slot of this part in the destination row
+};
+struct A2AParams {
+  A2APart part[3];
+  int n_parts;
+  int B, Tl, D, P, my_rank;
+  int dst_heads;              // heads per destination row
+  long dst_off;               // byte offset of the landing buffer inside every arena
+  const uint64_t* peers;
+};
+
+// sequence -> head: this rank's Tl tokens of every head go to the ranks that own the heads; destination
+// layout [B, P*Tl, dst_heads, D] with this rank's tokens at rows my_rank*Tl...   One warp per (b, t, peer).
+__global__ void a2a_push_kernel(A2AParams p) {
+  const int lane = threadIdx.x & 31;
+  const size_t n_items = (size_t)p.B * p.Tl * p.P;
+  const int vec_per_head = p.D / 8;                  // 16-byte vectors per head
+  for (size_t w = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); w < n_items; w += (size_t)gridDim.x * (blockDim.x >> 5)) {
+    const int peer = (int)(w % p.P);
+    const int t = (int)((w / p.P) % p.Tl);
+    const int b = (int)(w / ((size_t)p.P * p.Tl));
+    uint4* dst_row = (uint4*)(p.peers[peer] + p.dst_off) +
+                     (((size_t)b * p.P * p.Tl + (size_t)p.my_rank * p.Tl + t) * p.dst_heads) * vec_per_head;
+    for (int pi = 0; pi < p.n_parts; ++pi) {
+      const A2APart& a = p.part[pi];
+      const int nvec = a.n_local * vec_per_head;
+      for (int i = lane; i < nvec; i += 32) {
+        const int j = i / vec_per_head, c = i % vec_per_head;
+        const int sh = (peer * a.n_local + j) / a.rep;
+        const uint4 v = *((const uint4*)(a.src + ((size_t)b * p.Tl + t) * a.src_tok_stride + (size_t)sh * p.D) + c);
+        dst_row[(size_t)(a.dst_head_off + j) * vec_per_head + c] = v;
+      }
+    }
+  }
+}
+
+struct A2APullPart {
+  __nv_bfloat16* dst;         // local [B, Tl, *, D] view, element (b,t,h,:) at dst + (b*Tl+t)*dst_tok_stride + h*D
+  long dst_tok_stride;
+  int n_heads;                // heads of this part in the local (sequence-sharded) layout
+  int n_local;                // heads of this part per peer in the head-sharded layout
+  int rep;                    // replicas to sum (KV heads replicated over rep peers)
+  int src_head_off;           // first head slot of this part in the source row
+  int src_heads;              // heads per source row of this part's buffer
+  long src_off;               // byte offset of this part's head-sharded buffer inside every arena
+};
+struct A2APullParams {
+  A2APullPart part[3];
+  int n_parts;
+  int B, Tl, D, P, my_rank;
+  const uint64_t* peers;
+};
+
+// head -> sequence: every rank pulls, for its own Tl tokens, each head from the rank(s) that own it in the
+// head-sharded layout [B, P*Tl, src_heads, D], summing KV replicas in fp32.  One warp per (b, t, part, head).
+__global__ void a2a_pull_kernel(A2APullParams p) {
+  const int lane = threadIdx.x & 31;
+  int heads_total = 0;
+  for (int i = 0; i < p.n_parts; ++i) heads_total += p.part[i].n_heads;
+  const size_t n_items = (size_t)p.B * p.Tl * heads_total;
+  const int vec_per_head = p.D / 8;
+  for (size_t w = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); w < n_items; w += (size_t)gridDim.x * (blockDim.x >> 5)) {
+    int hh = (int)(w % heads_total);
+    const int t = (int)((w / heads_total) % p.Tl);
+    const int b = (int)(w / ((size_t)heads_total * p.Tl));
+    int pi = 0;
+    while (hh >= p.part[pi].n_heads) { hh -= p.part[pi].n_heads; ++pi; }
+    const A2APullPart& a = p.part[pi];
+    if (lane >= vec_per_head) continue;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int rr = 0; rr < a.rep; ++rr) {
+      const int peer = a.rep > 1 ? hh * a.rep + rr : hh / a.n_local;
+      const int j = a.rep > 1 ? 0 : hh % a.n_local;
+      const uint4* src_row = (const uint4*)(p.peers[peer] + a.src_off) +
+                             (((size_t)b * p.P * p.Tl + (size_t)p.my_rank * p.Tl + t) * a.src_heads) * vec_per_head;
+      const uint4 v = src_row[(size_t)(a.src_head_off + j) * vec_per_head + lane];
+      acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+      acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+    }
+    uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+    *((uint4*)(a.dst + ((size_t)b * p.Tl + t) * a.dst_tok_stride + (size_t)hh * p.D) + lane) = o;
+  }
+}
+
+// fp32 row vectors [B, H, Tl_pad] (sequence-sharded) -> [B, Hl, T_pad_total] on the head owners: used for the
+// attention backward's delta = rowsum(dO o O), computed where O lives.  dst row stride = dst_T.
+__global__ void a2a_push_rows_f32_kernel(const float* __restrict__ src, int B, int H, int Tl, int src_T, int n_local,
+                                         int P, int my_rank, long dst_off, int dst_T, const uint64_t* __restrict__ peers) {
+  const size_t n = (size_t)B * H * Tl;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i % Tl);
+    const int h = (int)((i / Tl) % H);
+    const int b = (int)(i / ((size_t)Tl * H));
+    const int peer = h / n_local, j = h % n_local;
+    float* dst = (float*)(peers[peer] + dst_off) + ((size_t)b * n_local + j) * dst_T + (size_t)my_rank * Tl + t;
+    *dst = src[((size_t)b * H + h) * src_T + t];
+  }
+}
+
+// ---------------------------------------------------------------------------- gradient all-reduce (two-shot)
+// Phase 1 (after a barrier): rank r owns slice r of the bucket; it reads slice r of every rank's bf16 staging
+// copy (grad * scale, written by cast_f32_bf16), sums in fp32 and writes the result as fp32 into its own
+// gradient buffer and as bf16 back into its own staging slice.
+// Phase 2 (after another barrier): every rank pulls the reduced bf16 slices of the other ranks into its fp32
+// gradient buffer.
+__global__ void allreduce_reduce_kernel(const uint64_t* __restrict__ peers, long stage_off, float* __restrict__ grad,
+                                        long n, int world, int my_rank) {
+  const long per = ((n + world - 1) / world + 7) / 8 * 8;
+  const long lo = per * my_rank, hi = min(n, lo + per);
+  const long nvec = (hi > lo) ? (hi - lo + 7) / 8 : 0;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      const int src = (my_rank + r) % world;         // stagger the peers so links are used evenly
+      const uint4 v = *((const uint4*)(peers[src] + stage_off) + (lo >> 3) + i);
+      acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+      acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+    }
+    const long e = lo + i * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) if (e + j < n) grad[e + j] = acc[j];
+    *((uint4*)(peers[my_rank] + stage_off) + (lo >> 3) + i) =
+        make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+  }
+}
+__global__ void allreduce_gather_kernel(const uint64_t* __restrict__ peers, long stage_off, float* __restrict__ grad,
+                                        long n, int world, int my_rank) {
+  const long per = ((n + world - 1) / world + 7) / 8 * 8;
+  const long nvec_total = (n + 7) / 8;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec_total; i += (long)gridDim.x * blockDim.x) {
+    const long e = i * 8;
+    const int owner = (int)(e / per);
+    if (owner == my_rank || owner >= world) continue;
+    const uint4 v = *((const uint4*)(peers[owner] + stage_off) + i);
+    const float f[8] = {bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y), bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w)};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) if (e + j < n) grad[e + j] = f[j];
+  }
+}
+
+static inline int grid_cap(size_t work, int block, int per_sm) {
+  size_t g = (work + block - 1) / block;
+  size_t cap = (size_t)sm_count() * per_sm;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace cpb
+
+using namespace cpb;
+
+extern "C" int cpb_barrier(const uint64_t* peers, long flag_off, int world, int my_rank, int epoch, double timeout_s,
+                           int* status, cudaStream_t stream) {
+  if (world > 32) return set_error(CPB_ERR_LIMIT, "barrier: at most 32 ranks");
+  const long spins = (long)(timeout_s * 1e9 / 150.0) + 1000;
+  barrier_kernel<<<1, 32, 0, stream>>>(peers, flag_off, world, my_rank, epoch, spins, status);
+  return check_launch("barrier");
+}
+
+// segs: device array of CopySeg (see ring_copy.cuh), sorted by chunk; ready[chunk] += n_ctas when a chunk landed.
+extern "C" int cpb_ring_gather(const void* segs, int n_segs, int* ready, int n_ctas, cudaStream_t stream) {
+  if (n_segs <= 0) return CPB_OK;
+  ring_gather_kernel<<<n_ctas, 256, 0, stream>>>((const CopySeg*)segs, n_segs, ready);
+  return check_launch("ring_gather");
+}
+
+// parts: up to 3 entries of {src ptr, src token stride, n_local, rep, dst_head_off} passed as flat arrays.
+extern "C" int cpb_a2a_push(const void* const* src, const long* src_tok_stride, const int* n_local, const int* rep,
+                            const int* dst_head_off, int n_parts, int B, int Tl, int D, int P, int my_rank,
+                            int dst_heads, long dst_off, const uint64_t* peers, cudaStream_t stream) {
+  if (n_parts < 1 || n_parts > 3 || (D % 8)) return set_error(CPB_ERR_ARG, "a2a_push: bad arguments");
+  A2AParams p;
+  for (int i = 0; i < n_parts; ++i) {
+    p.part[i].src = (const __nv_bfloat16*)src[i]; p.part[i].src_tok_stride = src_tok_stride[i];
+    p.part[i].n_local = n_local[i]; p.part[i].rep = rep[i] < 1 ? 1 : rep[i]; p.part[i].dst_head_off = dst_head_off[i];
+  }
+  p.n_parts = n_parts; p.B = B; p.Tl = Tl; p.D = D; p.P = P; p.my_rank = my_rank; p.dst_heads = dst_heads;
+  p.dst_off = dst_off; p.peers = peers;
+  a2a_push_kernel<<<grid_cap((size_t)B * Tl * P, 8, 8), 256, 0, stream>>>(p);
+  return check_launch("a2a_push");
+}
+
+extern "C" int cpb_a2a_pull(void* const* dst, const long* dst_tok_stride, const int* n_heads, const int* n_local,
+                            const int* rep, const int* src_head_off, const int* src_heads, const long* src_off,
+                            int n_parts, int B, int Tl, int D, int P, int my_rank, const uint64_t* peers,
+                            cudaStream_t stream) {
+  if (n_parts < 1 || n_parts > 3 || (D % 8) || D > 256) return set_error(CPB_ERR_ARG, "a2a_pull: bad arguments");
+  A2APullParams p;
+  size_t heads = 0;
+  for (int i = 0; i < n_parts; ++i) {
+    p.part[i].dst = (__nv_bfloat16*)dst[i]; p.part[i].dst_tok_stride = dst_tok_stride[i];
+    p.part[i].n_heads = n_heads[i]; p.part[i].n_local = n_local[i]; p.part[i].rep = rep[i] < 1 ? 1 : rep[i];
+    p.part[i].src_head_off = src_head_off[i]; p.part[i].src_heads = src_heads[i]; p.part[i].src_off = src_off[i];
+    heads += n_heads[i];
+  }
+  p.n_parts = n_parts; p.B = B; p.Tl = Tl; p.D = D; p.P = P; p.my_rank = my_rank; p.peers = peers;
+  a2a_pull_kernel<<<grid_cap((size_t)B * Tl * heads, 8, 8), 256, 0, stream>>>(p);
+  return check_launch("a2a_pull");
+}
+
+extern "C" int cpb_a2a_push_rows_f32(const float* src, int B, int H, int Tl, int src_T, int n_local, int P, int my_rank,
+                                     long dst_off, int dst_T, const uint64_t* peers, cudaStream_t stream) {
+  a2a_push_rows_f32_kernel<<<grid_cap((size_t)B * H * Tl, 256, 8), 256, 0, stream>>>(src, B, H, Tl, src_T, n_local, P, my_rank, dst_off, dst_T, peers);
+  return check_launch("a2a_push_rows_f32");
+}
+
+extern "C" int cpb_allreduce_reduce(const uint64_t* peers, long stage_off, float* grad, long n, int world, int my_rank,
+                                    int n_ctas, cudaStream_t stream) {
+  if (n <= 0) return CPB_OK;
+  allreduce_reduce_kernel<<<n_ctas, 512, 0, stream>>>(peers, stage_off, grad, n, world, my_rank);
+  return check_launch("allreduce_reduce");
+}
+extern "C" int cpb_allreduce_gather(const uint64_t* peers, long stage_off, float* grad, long n, int world, int my_rank,
+                                    int n_ctas, cudaStream_t stream) {
+  if (n <= 0) return CPB_OK;
+  allreduce_gather_kernel<<<n_ctas, 512, 0, stream>>>(peers, stage_off, grad, n, world, my_rank);
+  return check_launch("allreduce_gather");
+}

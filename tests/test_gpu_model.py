@@ -88,3 +88,20 @@ def test_model_step_matches_cpu_oracle(family, recompute):
     assert lg[-1] < lg[0]
     ng, nc = float(gpu.last_grad_norm), float(cpu.last_grad_norm)
     assert abs(ng - nc) / nc < 0.1, (ng, nc)
+
+
+def test_recompute_grads_identical():
+    """Activation recomputation must not change any gradient nor leave gradients outside the flat buffer."""
+    from context_parallelism_b200.config import Config
+    from context_parallelism_b200.engine import TrainEngine
+    kw = dict(n_embd=256, n_layer=2, n_head=4, head_dim=64, vocab_size=1000, T=384, B=2, max_steps=20, warmup_steps=1,
+              checkpointing=False, n_kv_head=2, ffn_hidden=512)
+    tok = torch.randint(0, 1000, (2, 385), generator=torch.Generator().manual_seed(3)).to(dev())
+    grads = {}
+    for rc in ("none", "selective"):
+        eng = TrainEngine(Config.from_env("llama", 1, env={}).replace(**kw, recompute=rc), dev())
+        eng.forward_backward(tok[:, :-1], tok[:, 1:])
+        assert all(p.grad is None for p in eng.model.parameters())
+        grads[rc] = eng.flat.grad.clone()
+    assert float(grads["none"].norm()) > 0
+    assert_close(grads["selective"], grads["none"], cos=0.99999, name="flat grads")

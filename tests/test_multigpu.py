@@ -1,0 +1,31 @@
+"""Context parallelism on real GPUs (one process per GPU, NCCL + the peer-memory kernels): fused and
+NCCL-baseline transports of ring / Ulysses / hybrid reproduce the unsharded run."""
+import pytest
+import torch
+
+from test_cp_cpu_gloo import run_worker
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.parametrize("rotator", ["fused", "p2p"])
+def test_ring_2gpu(rotator):
+    run_worker(2, "--mode", "ring", "--rotator", rotator, "--T", 1024, "--tol", 3e-2, device="cuda")
+
+
+@pytest.mark.parametrize("rotator,kv", [("fused", 2), ("fused", 1), ("alltoall", 2)])
+def test_ulysses_2gpu(rotator, kv):
+    run_worker(2, "--mode", "ulysses", "--rotator", rotator, "--kv", kv, "--T", 1024, "--tol", 3e-2, device="cuda")
+
+
+def test_ring_fused_gpt2_recompute_2gpu():
+    run_worker(2, "--mode", "ring", "--rotator", "fused", "--family", "gpt2", "--T", 1024, "--tol", 3e-2,
+               "--recompute", "selective", device="cuda")
+
+
+@pytest.mark.skipif(NGPU < 4, reason="needs 4 GPUs")
+@pytest.mark.parametrize("mode,extra", [("ring", []), ("ulysses", ["--kv", 2]), ("hybrid", ["--ulysses", 2]),
+                                        ("ring", ["--cp", 2])])
+def test_fused_4gpu(mode, extra):
+    run_worker(4, "--mode", mode, "--rotator", "fused", "--T", 2048, "--tol", 3e-2, *extra, device="cuda")
