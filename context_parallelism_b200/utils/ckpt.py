@@ -1,0 +1,188 @@
+"""Named-record weight files and run-numbered checkpoints with auto-resume.
+
+Record format (byte-compatible with the reference's named-init files,
+Scripts/Pytorch/gpt2_cp_attnstyle_fp32.py:752-767, reader Scripts/Blutrain/gpt2_cp_test.cpp:851-933):
+repeated ``int32 name_len | name bytes | int32 ndim | int64 dims[ndim] | float32 data`` in PyTorch layout
+(Linear weights ``[out, in]``), little endian, no header.
+
+Checkpoints reuse the same record stream: the model tensors under their reference names, then
+``opt.m.<name>`` / ``opt.v.<name>`` Adam moments, then a ``__meta__`` record ``[step, loss, run]``.  Files are
+``<dir>/<prefix>_run<N>/<prefix>_run<N>_step_<S>.ckpt``; rank 0 saves, every rank loads, the newest
+``keep`` files are kept, and the run to resume is chosen like the reference does
+(Scripts/Blutrain/bluscriptCP.cpp:1049-1088): ``CP_CKPT_RESUME=<N>`` forces a run, ``CP_CKPT_NEW_RUN=1``
+forces a fresh one, otherwise the highest run whose last step is below ``max_steps``.  Checkpoints do not
+depend on sequence length or world size.
+"""
+from __future__ import annotations
+
+import os
+import re
+import struct
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+
+def write_named(path: str, tensors: Iterable[Tuple[str, torch.Tensor]]) -> int:
+    n = 0
+    tmp = path + ".tmp"
+    with open(tmp, "wb") as f:
+        for name, t in tensors:
+            arr = t.detach().to(torch.float32).cpu().contiguous().numpy()
+            nm = name.encode()
+            f.write(struct.pack("<i", len(nm)))
+            f.write(nm)
+            f.write(struct.pack("<i", arr.ndim))
+            for d in arr.shape:
+                f.write(struct.pack("<q", int(d)))
+            f.write(arr.tobytes())
+            n += 1
+    os.replace(tmp, path)
+    return n
+
+
+def read_named(path: str) -> Dict[str, torch.Tensor]:
+    out: Dict[str, torch.Tensor] = {}
+    with open(path, "rb") as f:
+        data = f.read()
+    off, size = 0, len(data)
+    while off < size:
+        (nl,) = struct.unpack_from("<i", data, off); off += 4
+        if nl <= 0 or nl > 4096:
+            raise ValueError(f"{path}: corrupt record at byte {off - 4}")
+        name = data[off:off + nl].decode(); off += nl
+        (nd,) = struct.unpack_from("<i", data, off); off += 4
+        dims = struct.unpack_from(f"<{nd}q", data, off); off += 8 * nd
+        cnt = int(np.prod(dims)) if nd else 1
+        arr = np.frombuffer(data, dtype="<f4", count=cnt, offset=off).reshape(dims)
+        off += 4 * cnt
+        out[name] = torch.from_numpy(arr.copy())
+    return out
+
+
+def _split_fused(model, flat) -> List[Tuple[str, torch.Tensor]]:
+    """Model tensors under reference names, taken from the fp32 masters."""
+    masters = flat.named_master()
+    by_param = {id(p): masters[name] for name, p, _, _ in flat.entries}
+    out = []
+    for name, view in model.named_tensors().items():
+        base = view._base if view._base is not None else view
+        m = by_param.get(id(base))
+        if m is None:      # e.g. tied lm_head alias
+            continue
+        if view._base is not None:
+            off = view.storage_offset() - base.storage_offset()
+            rows = off // base.shape[1]
+            m = m[rows:rows + view.shape[0]]
+        out.append((name, m))
+    return out
+
+
+def save_named_init(path: str, model, flat) -> int:
+    return write_named(path, _split_fused(model, flat))
+
+
+def load_named_into(model, flat, tensors: Dict[str, torch.Tensor], strict: bool = True) -> int:
+    """Copy records into the fp32 masters (and refresh the bf16 compute copies).  Vocabulary rows beyond the
+    file's row count stay zero (padding)."""
+    by_param = {id(p): (name, p) for name, p, _, _ in flat.entries}
+    masters = flat.named_master()
+    n = 0
+    for name, view in model.named_tensors().items():
+        if name not in tensors:
+            if strict:
+                raise KeyError(f"missing tensor {name!r} in weight file")
+            continue
+        src = tensors[name]
+        base = view._base if view._base is not None else view
+        ent = by_param.get(id(base))
+        if ent is None:
+            continue
+        m = masters[ent[0]]
+        if view._base is not None:
+            off = view.storage_offset() - base.storage_offset()
+            rows = off // base.shape[1]
+            m = m[rows:rows + view.shape[0]]
+        if src.dim() == 2 and m.dim() == 2 and src.shape[0] < m.shape[0] and src.shape[1] == m.shape[1]:
+            m[: src.shape[0]].copy_(src)
+        else:
+            if tuple(src.shape) != tuple(m.shape):
+                raise ValueError(f"{name}: file shape {tuple(src.shape)} != model shape {tuple(m.shape)}")
+            m.copy_(src)
+        n += 1
+    flat.sync_compute_copy()
+    return n
+
+
+# ------------------------------------------------------------------ run-numbered checkpoints
+_RUN_RE = re.compile(r"_run(\d+)$")
+_STEP_RE = re.compile(r"_step_(\d+)\.ckpt$")
+
+
+class CheckpointManager:
+    def __init__(self, root: str, prefix: str, keep: int = 6, rank: int = 0):
+        self.root, self.prefix, self.keep, self.rank = root, prefix, keep, rank
+        self.run: Optional[int] = None
+
+    def run_dir(self, run: int) -> str:
+        return os.path.join(self.root, f"{self.prefix}_run{run}")
+
+    def list_runs(self) -> Dict[int, List[int]]:
+        runs: Dict[int, List[int]] = {}
+        if not os.path.isdir(self.root):
+            return runs
+        for d in os.listdir(self.root):
+            m = _RUN_RE.search(d)
+            if not m or not d.startswith(self.prefix):
+                continue
+            steps = []
+            for f in os.listdir(os.path.join(self.root, d)):
+                s = _STEP_RE.search(f)
+                if s:
+                    steps.append(int(s.group(1)))
+            runs[int(m.group(1))] = sorted(steps)
+        return runs
+
+    def resolve_run(self, max_steps: int, new_run: bool = False, resume: int = -1) -> Tuple[int, bool]:
+        """Returns ``(run_number, resuming)``.  Call on rank 0 and broadcast the result."""
+        runs = self.list_runs()
+        if resume >= 0:
+            return resume, bool(runs.get(resume))
+        if not new_run:
+            for r in sorted(runs, reverse=True):
+                if runs[r] and runs[r][-1] < max_steps:
+                    return r, True
+        return (max(runs) + 1 if runs else 0), False
+
+    def path(self, run: int, step: int) -> str:
+        return os.path.join(self.run_dir(run), f"{self.prefix}_run{run}_step_{step}.ckpt")
+
+    def save(self, run: int, step: int, model, flat, opt, loss: float) -> Optional[str]:
+        if self.rank != 0:
+            return None
+        os.makedirs(self.run_dir(run), exist_ok=True)
+        recs = _split_fused(model, flat)
+        for name, t in opt.state_dict().items():
+            recs.append(("opt." + name, t))
+        recs.append(("__meta__", torch.tensor([float(step), float(loss), float(run)])))
+        p = self.path(run, step)
+        write_named(p, recs)
+        steps = self.list_runs().get(run, [])
+        for s in steps[:-self.keep] if self.keep > 0 else []:
+            try:
+                os.remove(self.path(run, s))
+            except OSError:
+                pass
+        return p
+
+    def load_latest(self, run: int, model, flat, opt) -> Tuple[int, float]:
+        """Load the newest checkpoint of ``run`` on every rank; returns ``(step, loss)`` or ``(0, nan)``."""
+        steps = self.list_runs().get(run, [])
+        if not steps:
+            return 0, float("nan")
+        recs = read_named(self.path(run, steps[-1]))
+        load_named_into(model, flat, recs, strict=True)
+        opt.load_state_dict({k[4:]: v for k, v in recs.items() if k.startswith("opt.")})
+        meta = recs.get("__meta__")
+        return (int(meta[0]), float(meta[1])) if meta is not None else (steps[-1], float("nan"))

@@ -43,7 +43,8 @@ struct Watchdog {
       const auto now = Clock::now();
       for (Work* w : live) {
         if (w->state.load() != W_PENDING) continue;
-        cudaError_t e = w->ev ? cudaEventQuery(w->ev) : cudaSuccess;
+        // a handle without an event is completed explicitly by its owner (cpb_work_complete)
+        cudaError_t e = w->ev ? cudaEventQuery(w->ev) : cudaErrorNotReady;
         if (e == cudaSuccess) w->state.store(W_DONE);
         else if (e != cudaErrorNotReady) { cudaGetLastError(); w->state.store(W_ERROR); }
         else if (w->has_deadline && now > w->deadline) { w->state.store(W_TIMED_OUT); timeouts++; }
