@@ -5,7 +5,8 @@
 //   S^T  = K Q^T            (smem x smem)          P^T  = exp2(S^T*c - LSE)         (registers)
 //   dP^T = V dO^T           (smem x smem)          dS^T = P^T o (dP^T - Delta) * scale
 //   dV  += P^T  dO          (tmem x smem)          dK  += dS^T Q      (tmem x smem)
-//   dQ   = dS K             (smem x smem, dS^T staged M-major in shared memory) -> fp32 red.add
+//   dQ   = dS K             (smem x smem, dS^T staged M-major in shared memory) -> staged in shared memory
+//                           and added to the fp32 dQ buffer by TMA reduce (cp.reduce.async.bulk.tensor .add)
 //
 // Computing the transposed score tile puts K/V rows in tensor-memory lanes, so P^T and dS^T feed the
 // dV / dK products directly as tensor-memory A operands and dK / dV never leave tensor memory until
@@ -18,15 +19,16 @@
 // Replaces mem_efficient_bwd_unified_kernel_exp11 (context_parallel/AttentionBackward.cu:300-541) and
 // gqa_fused_rope_bwd_dQ / _dKdV (context_parallel/GQA_fused_bwd_sm103_cp.cu:135-565).
 //
-// Warp roles (320 threads): 0 = TMA loader, 1 = MMA issuer, 2..5 = softmax-gradient warps (thread = K/V
-// row), 6..9 = dQ drain warps (thread = query row).
+// Warp roles (448 threads): 0 = TMA loader, 1 = MMA issuer, 2..9 = softmax-gradient warps (two threads per K/V
+// row, 64 query columns each, so every scheduler has two such warps to hide tensor-memory and MUFU latency),
+// 10..13 = dQ drain warps (thread = query row).
 #include "common.cuh"
 #include "host_utils.h"
 
 namespace cpb {
 
 constexpr int FB_T = 128;            // tile edge (queries and keys)
-constexpr int FB_THREADS = 320;
+constexpr int FB_THREADS = 448;
 
 struct BwdParams {
   int B, Tq, Tk, Hq, Hkv, Tq_pad;
@@ -35,7 +37,7 @@ struct BwdParams {
   const float* lse2;        // [B,Hq,Tq_pad] LSE * log2(e), +inf in the padding
   const float* delta;       // [B,Hq,Tq_pad] rowsum(dO o O), 0 in the padding
   const int* q_pos;         // [Tq_pad] global positions, INT_MAX in the padding
-  float* dq;                // [B,Tq,Hq,D] fp32, accumulated with red.add
+  float* dq;                // [B,Tq,Hq,D] fp32, accumulated by TMA reduce-add
   void* dk; void* dv;       // [B,Tk,Hkv,D] bf16 (store) or fp32 (accumulate)
   int dkv_f32_accumulate;
   // fused ring (dkv_f32_accumulate == 2): K/V row kidx belongs to chunk c = kidx / route_rows, owned by some
@@ -57,7 +59,8 @@ struct BwdSmem {
   static constexpr int Q_OFF = 2 * TILE;
   static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
   static constexpr int DS_OFF = DO_OFF + STAGES * TILE;           // dS^T: 128 x 128 bf16, M-major
-  static constexpr int VEC_OFF = DS_OFF + FB_T * FB_T * 2;        // per stage: lse2[128], delta[128], qpos[128]
+  static constexpr int DQS_OFF = DS_OFF + FB_T * FB_T * 2;        // dQ staging: 2 boxes of 128 rows x 32 fp32, 128B-swizzled
+  static constexpr int VEC_OFF = DQS_OFF + 2 * FB_T * 128;        // per stage: lse2[128], delta[128], qpos[128]
   static constexpr int BAR_OFF = VEC_OFF + STAGES * 3 * 512;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
@@ -73,7 +76,8 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 template <int D>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, BwdParams p) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                 const __grid_constant__ CUtensorMap tmDQ, BwdParams p) {
   using L = BwdSmem<D>;
   constexpr int ST = L::STAGES;
   constexpr int DH = D / 64;
@@ -104,7 +108,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
-    mbar_init(s_full, 1); mbar_init(p_full, 128); mbar_init(dq_full, 1); mbar_init(dq_empty, 128); mbar_init(acc_done, 1);
+    mbar_init(s_full, 1); mbar_init(p_full, 256); mbar_init(dq_full, 1); mbar_init(dq_empty, 128); mbar_init(acc_done, 1);
     *abort_flag = 0;
     *qt_start_s = num_q_tiles;
     fence_mbar_init();
@@ -189,10 +193,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < FB_T / 16; ++k)      // dV += P^T dO : contraction over the 128 queries
-            umma_ts(tmem_base + DV_COL, tmem_base + ST_COL + k * 8, make_sdesc(sDO + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
+            umma_ts(tmem_base + DV_COL, tmem_base + ST_COL + (k >> 2) * 64 + (k & 3) * 8, make_sdesc(sDO + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
 #pragma unroll
           for (int k = 0; k < FB_T / 16; ++k)      // dK += dS^T Q
-            umma_ts(tmem_base + DK_COL, tmem_base + DPT_COL + k * 8, make_sdesc(sQ + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
+            umma_ts(tmem_base + DK_COL, tmem_base + DPT_COL + (k >> 2) * 64 + (k & 3) * 8, make_sdesc(sQ + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
 #pragma unroll
           for (int k = 0; k < FB_T / 16; ++k)      // dQ = dS K : contraction over the 128 keys
             umma_ss(tmem_base + DQ_COL, make_sdesc(sDS + k * 2048, FB_T * 128, 1024), make_sdesc(sK + k * 2048, FB_T * 128, 1024), idesc_dq, k != 0);
@@ -202,15 +206,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(acc_done);
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 10) {
     // ------------------------------------------------------------------ softmax-gradient warps
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;                   // which 64 query columns of the tile this thread owns
+    const int cbase = half * 64;
     const int r = quarter * 32 + lane;                  // K/V row inside the tile
     const int kidx = k0 + r;
     const bool k_valid = kidx < p.Tk;
     const int kpos = p.k_off + kidx;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    uint8_t* ds_row = smem + L::DS_OFF + r * 128;
+    uint8_t* ds_row = smem + L::DS_OFF + half * (FB_T * 128) + r * 128;
     bool alive = true;
     for (int i = 0; i < n_it && alive; ++i) {
       const int st = i % ST;
@@ -219,42 +225,54 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { alive = false; break; }
       tc_fence_after();
-      const float* lse2 = (const float*)(smem + L::VEC_OFF + st * 1536);
+      const float* lse2 = (const float*)(smem + L::VEC_OFF + st * 1536) + cbase;
       const float* delta = lse2 + 128;
       const int* qpos = (const int*)(lse2 + 256);
       const bool need_mask = p.causal && (p.k_off + k0 + FB_T - 1 > qpos[0]);
-#pragma unroll 1
-      for (int c = 0; c < FB_T; c += 32) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(t_lane + ST_COL + c, s);
-        tmem_ld32(t_lane + DPT_COL + c, dp);
-        tmem_wait_ld();
-        uint32_t pk[16], dk_[16];
+      // 4 chunks of 16 columns; the tensor-memory loads of chunk ch+1 are in flight while chunk ch is processed.
+      // P^T / dS^T (bf16, two per column) go back into the first 32 columns of this thread's own 64-column
+      // span, always behind the columns already consumed.
+      uint32_t sv[4][16], dpv[4][16];
+      tmem_ld16(t_lane + ST_COL + cbase, sv[0]);
+      tmem_ld16(t_lane + DPT_COL + cbase, dpv[0]);
+      tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float p0 = ex2f(fmaf(__uint_as_float(s[j]), p.scale_log2, -lse2[c + j]));
-          float p1 = ex2f(fmaf(__uint_as_float(s[j + 1]), p.scale_log2, -lse2[c + j + 1]));
-          if (!k_valid) { p0 = 0.f; p1 = 0.f; }
+      for (int ch = 0; ch < 4; ++ch) {
+        if (ch < 3) {
+          tmem_ld16(t_lane + ST_COL + cbase + 16 * (ch + 1), sv[ch + 1]);
+          tmem_ld16(t_lane + DPT_COL + cbase + 16 * (ch + 1), dpv[ch + 1]);
+        }
+        uint32_t pk[8], dk_[8];
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          const float4 l4 = *(const float4*)(lse2 + ch * 16 + j);
+          const float4 d4 = *(const float4*)(delta + ch * 16 + j);
+          float p0 = ex2f(fmaf(__uint_as_float(sv[ch][j]), p.scale_log2, -l4.x));
+          float p1 = ex2f(fmaf(__uint_as_float(sv[ch][j + 1]), p.scale_log2, -l4.y));
+          float p2 = ex2f(fmaf(__uint_as_float(sv[ch][j + 2]), p.scale_log2, -l4.z));
+          float p3 = ex2f(fmaf(__uint_as_float(sv[ch][j + 3]), p.scale_log2, -l4.w));
+          if (!k_valid) { p0 = p1 = p2 = p3 = 0.f; }
           if (need_mask) {
-            if (kpos > qpos[c + j]) p0 = 0.f;
-            if (kpos > qpos[c + j + 1]) p1 = 0.f;
+            const int4 q4 = *(const int4*)(qpos + ch * 16 + j);
+            if (kpos > q4.x) p0 = 0.f;
+            if (kpos > q4.y) p1 = 0.f;
+            if (kpos > q4.z) p2 = 0.f;
+            if (kpos > q4.w) p3 = 0.f;
           }
-          const float d0 = p0 * (__uint_as_float(dp[j]) - delta[c + j]) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dp[j + 1]) - delta[c + j + 1]) * p.scale;
-          pk[j >> 1] = pack_bf16(p0, p1);
-          dk_[j >> 1] = pack_bf16(d0, d1);
+          const float e0 = p0 * (__uint_as_float(dpv[ch][j]) - d4.x) * p.scale;
+          const float e1 = p1 * (__uint_as_float(dpv[ch][j + 1]) - d4.y) * p.scale;
+          const float e2 = p2 * (__uint_as_float(dpv[ch][j + 2]) - d4.z) * p.scale;
+          const float e3 = p3 * (__uint_as_float(dpv[ch][j + 3]) - d4.w) * p.scale;
+          pk[j >> 1] = pack_bf16(p0, p1); pk[(j >> 1) + 1] = pack_bf16(p2, p3);
+          dk_[j >> 1] = pack_bf16(e0, e1); dk_[(j >> 1) + 1] = pack_bf16(e2, e3);
         }
-        tmem_st16(t_lane + ST_COL + (c >> 1), pk);
-        tmem_st16(t_lane + DPT_COL + (c >> 1), dk_);
-        // dS^T row r, queries c..c+31 -> shared memory, M-major 128B-swizzled: 16-byte chunk q/8 of the
-        // 64-query group q/64 goes to chunk position (chunk ^ (r & 7)).
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const int q = c + ch * 8;
-          const int grp = q >> 6, chunk = (q & 63) >> 3;
-          uint4 val = make_uint4(dk_[ch * 4], dk_[ch * 4 + 1], dk_[ch * 4 + 2], dk_[ch * 4 + 3]);
-          *(uint4*)(ds_row + grp * (FB_T * 128) + ((chunk ^ (r & 7)) << 4)) = val;
-        }
+        tmem_st8(t_lane + ST_COL + cbase + ch * 8, pk);
+        tmem_st8(t_lane + DPT_COL + cbase + ch * 8, dk_);
+        // dS^T row r -> shared memory, M-major 128B-swizzled: 16-byte chunk (q % 64) / 8 of this thread's
+        // 64-query group goes to chunk position (chunk ^ (r & 7)).
+        *(uint4*)(ds_row + (((2 * ch) ^ (r & 7)) << 4)) = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
+        *(uint4*)(ds_row + (((2 * ch + 1) ^ (r & 7)) << 4)) = make_uint4(dk_[4], dk_[5], dk_[6], dk_[7]);
+        if (ch < 3) tmem_wait_ld();
       }
       tmem_wait_st();
       fence_proxy_async_smem();
@@ -263,7 +281,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     // final: dK, dV -> global
     if (n_it == 0) {
-      if (!p.dkv_f32_accumulate && k_valid) {
+      if (!p.dkv_f32_accumulate && k_valid && half == 0) {
         __nv_bfloat16* dkr = (__nv_bfloat16*)p.dk + (((size_t)b * p.Tk + kidx) * p.Hkv + hkv) * D;
         __nv_bfloat16* dvr = (__nv_bfloat16*)p.dv + (((size_t)b * p.Tk + kidx) * p.Hkv + hkv) * D;
 #pragma unroll
@@ -276,7 +294,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_after();
         const size_t off = (((size_t)b * p.Tk + (k_valid ? kidx : 0)) * p.Hkv + hkv) * D;
 #pragma unroll 1
-        for (int which = 0; which < 2; ++which) {
+        for (int which = half; which <= half; ++which) {          // first warp group drains dK, second dV
           const uint32_t col = which ? DV_COL : DK_COL;
           void* base = which ? p.dv : p.dk;
 #pragma unroll 1
@@ -319,32 +337,50 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ dQ drain warps (6..9)
+    // ------------------------------------------------------------------ dQ drain warps (10..13)
+    // tensor memory -> registers -> 128B-swizzled fp32 staging tile -> TMA reduce-add into the global fp32 dQ
+    // (rows past the end of the sequence are clipped by the tensor map).
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;                  // query row inside the tile
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    uint8_t* stage = smem + L::DQS_OFF;
+    const bool issuer = (warp == 10 && lane == 0);
+    if (issuer) tma_prefetch_desc(&tmDQ);
     for (int i = 0; i < n_it; ++i) {
       bool ok = mbar_wait(dq_full, i & 1, abort_flag, p.status, 1100);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const int hq = hkv * G + i / n_qt;
-      const int qi = (qt_start + i % n_qt) * FB_T + r;
-      float* dst = p.dq + (((size_t)b * p.Tq + (qi < p.Tq ? qi : 0)) * p.Hq + hq) * D;
+      const int q0 = (qt_start + i % n_qt) * FB_T;
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(t_lane + DQ_COL + c, v);
-        tmem_wait_ld();
-        if (qi < p.Tq) {
+      for (int rnd = 0; rnd < D / 64; ++rnd) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            red_add_v4(dst + c + j, __uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+        for (int bx = 0; bx < 2; ++bx) {
+          uint32_t v[32];
+          tmem_ld32(t_lane + DQ_COL + rnd * 64 + bx * 32, v);
+          tmem_wait_ld();
+          uint8_t* rowp = stage + bx * (FB_T * 128) + r * 128;
+#pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4)
+            *(uint4*)(rowp + ((c4 ^ (r & 7)) << 4)) = make_uint4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
         }
+        if (rnd == D / 64 - 1) { tc_fence_before(); mbar_arrive(dq_empty); }     // tensor-memory dQ is free again
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 5, 128;" ::: "memory");
+        if (issuer) {
+#pragma unroll
+          for (int bx = 0; bx < 2; ++bx)
+            asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                         ::"l"((uint64_t)&tmDQ), "r"(smem_u32(stage + bx * (FB_T * 128))), "r"(rnd * 64 + bx * 32), "r"(hq), "r"(q0), "r"(b)
+                         : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        }
+        asm volatile("bar.sync 5, 128;" ::: "memory");                             // staging may be overwritten
       }
-      tc_fence_before();
-      mbar_arrive(dq_empty);
     }
+    if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   tc_fence_before();
@@ -432,6 +468,13 @@ extern "C" int cpb_flash_bwd(const void* q, const void* k, const void* v, const 
   if ((rc = make_tmap4(&tk, k, D, Hkv, Tk, B, k_sh, k_st, k_sb)) != CPB_OK) return rc;
   if ((rc = make_tmap4(&tv, v, D, Hkv, Tk, B, k_sh, k_st, k_sb)) != CPB_OK) return rc;
   if ((rc = make_tmap4(&tdo, dout, D, Hq, Tq, B, D, (long)Hq * D, (long)Tq * Hq * D)) != CPB_OK) return rc;
+  CUtensorMap tdq;
+  {
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hq, (uint64_t)Tq, (uint64_t)B};
+    uint64_t strides[4] = {0, (uint64_t)D * 4, (uint64_t)Hq * D * 4, (uint64_t)Tq * Hq * D * 4};
+    uint32_t box[4] = {32, 1, (uint32_t)FB_T, 1};
+    if ((rc = encode_tmap(&tdq, dq, 4, 4, dims, strides, box, 1)) != CPB_OK) return rc;
+  }
   BwdParams p;
   p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv; p.Tq_pad = Tq_pad; p.causal = causal; p.k_off = k_off;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
@@ -444,11 +487,11 @@ extern "C" int cpb_flash_bwd(const void* q, const void* k, const void* v, const 
   if (D == 64) {
     static bool cfg = false;
     if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::TOTAL)); cfg = true; }
-    flash_bwd_kernel<64><<<grid, FB_THREADS, BwdSmem<64>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+    flash_bwd_kernel<64><<<grid, FB_THREADS, BwdSmem<64>::TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);
   } else {
     static bool cfg = false;
     if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::TOTAL)); cfg = true; }
-    flash_bwd_kernel<128><<<grid, FB_THREADS, BwdSmem<128>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+    flash_bwd_kernel<128><<<grid, FB_THREADS, BwdSmem<128>::TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);
   }
   return check_launch("flash_bwd");
 }

@@ -1,6 +1,8 @@
 // Flash-attention forward for sm_100a: S = Q K^T and O += P V on tcgen05 tensor cores with S, P and O
 // resident in tensor memory; K/V tiles streamed by TMA (no multicast) through a 2-stage ring; online
-// softmax with lazy rescaling in four softmax warps (one thread per query row).
+// softmax with lazy rescaling in eight softmax warps (two threads per query row, 64 key columns each, row
+// maxima exchanged through shared memory), so each scheduler has enough warps to hide MUFU and tensor-memory
+// latency.
 //
 // One kernel serves every attention mode of the framework:
 //   * local causal / non-causal attention with GQA (Ulysses, world size 1);
@@ -25,7 +27,7 @@ namespace cpb {
 
 constexpr int FA_BQ = 128;
 constexpr int FA_BK = 128;
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;
 constexpr int FA_STAGES = 2;
 
 struct FwdParams {
@@ -63,7 +65,8 @@ struct FwdSmem {
   static constexpr int K_OFF = Q_BYTES;
   static constexpr int V_OFF = K_OFF + FA_STAGES * KV_BYTES;
   static constexpr int BAR_OFF = V_OFF + FA_STAGES * KV_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int XCH_OFF = BAR_OFF + 256;            // [2 tiles][2 halves][128 rows] fp32 row-max exchange
+  static constexpr int TOTAL = XCH_OFF + 2048 + 1024;
 };
 
 // Bounded acquire-spin on a readiness flag in global memory (written by a copy kernel or a peer).
@@ -136,7 +139,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_init(o_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -211,7 +214,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < FA_BK / 16; ++k) {
             // A = P (bf16, 8 tensor-memory columns per 16 keys); B = V tile, N-major: 16 key rows = 2 KB
-            umma_ts(o_tmem, s_tmem + k * 8, make_sdesc(sv + k * 2048, FA_BK * 128, 1024), idesc_pv, (j | k) != 0);
+            umma_ts(o_tmem, s_tmem + (k >> 2) * 64 + (k & 3) * 8, make_sdesc(sv + k * 2048, FA_BK * 128, 1024), idesc_pv, (j | k) != 0);
           }
           umma_commit(&kv_empty[st]);
           if (j + 1 < n_kv) {
@@ -225,15 +228,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax + epilogue (warps 2..5)
+    // ------------------------------------------------------------------ softmax + epilogue (warps 2..9)
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;                  // which 64 key columns of every tile this thread owns
+    const int cbase = half * 64;
     const int row = quarter * 32 + lane;
     const int qi = q0 + row;
     const bool row_valid = qi < p.Tq;
     const int my_qpos = row_valid ? (p.q_pos ? p.q_pos[qi] : qi) : 0x7fffffff;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float* xch = (float*)(smem + L::XCH_OFF);
     float m_used = -INFINITY;    // running max (scaled, log2 domain) the accumulators are relative to
-    float l = 0.f;
+    float l = 0.f;               // this thread's share of the row sum
     bool alive = n_kv > 0;
     for (int j = 0; j < n_kv && alive; ++j) {
       bool ok = mbar_wait(s_full, j & 1, abort_flag, p.status, 700);
@@ -244,22 +250,29 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int k0 = (jj >= n_kv ? jj - n_kv : jj) * FA_BK;
       const bool need_mask = (k0 + FA_BK > p.Tk) || (p.causal && (k0 + FA_BK - 1 + p.k_off > qpos_min));
       const int kmax_causal = p.causal ? (my_qpos - p.k_off) : 0x7fffffff;   // last visible index
-      const int kmax = min(kmax_causal, p.Tk - 1) - k0;                       // last visible column of this tile
-      // pass 1: row maximum
+      const int kmax = min(kmax_causal, p.Tk - 1) - k0 - cbase;               // last visible column of my span
+      // this thread's 64 scores, one tensor-memory round trip
+      uint32_t sv[4][16];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) tmem_ld16(t_lane + cbase + 16 * ch, sv[ch]);
+      tmem_wait_ld();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < FA_BK; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(t_lane + c, v);
-        tmem_wait_ld();
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) if (c + i <= kmax) mx = fmaxf(mx, __uint_as_float(v[i]));
-        } else {
+        for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-        }
+          for (int i = 0; i < 16; ++i) if (ch * 16 + i <= kmax) mx = fmaxf(mx, __uint_as_float(sv[ch][i]));
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(sv[ch][i]));
       }
+      // row maximum over both halves: exchange through shared memory with the partner warp (same rows)
+      float* slot = xch + (j & 1) * 256;
+      slot[half * 128 + row] = mx;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      mx = fmaxf(mx, slot[(half ^ 1) * 128 + row]);
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       // lazy rescale: keep the old reference maximum unless it fell behind by more than 2^8
       const bool need = (m_new > m_used + 8.f);
@@ -270,8 +283,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         l *= alpha;
       }
       if (j > 0 && __any_sync(0xffffffffu, need)) {
+        // each thread of the pair rescales its own half of the O columns
 #pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
+        for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
           uint32_t v[32];
           tmem_ld32(t_lane + O_COL + c, v);
           tmem_wait_ld();
@@ -280,26 +294,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st32(t_lane + O_COL + c, v);
         }
       }
-      // pass 2: p = exp2(s*scale - m), row sum, bf16 P written behind the S columns already consumed
+      // p = exp2(s*scale - m); bf16 P (two per column) goes back into the first 32 columns of my own span
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-#pragma unroll 1
-      for (int c = 0; c < FA_BK; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(t_lane + c, v);
-        tmem_wait_ld();
-        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_sub));
-          float p1 = ex2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_sub));
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t pk[8];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          float p0 = ex2f(fmaf(__uint_as_float(sv[ch][i]), p.scale_log2, -m_sub));
+          float p1 = ex2f(fmaf(__uint_as_float(sv[ch][i + 1]), p.scale_log2, -m_sub));
           if (need_mask) {
-            if (c + i > kmax) p0 = 0.f;
-            if (c + i + 1 > kmax) p1 = 0.f;
+            if (ch * 16 + i > kmax) p0 = 0.f;
+            if (ch * 16 + i + 1 > kmax) p1 = 0.f;
           }
           l += p0 + p1;
           pk[i >> 1] = pack_bf16(p0, p1);
         }
-        tmem_st16(t_lane + (c >> 1), pk);
+        tmem_st8(t_lane + cbase + ch * 8, pk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -307,6 +318,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     // epilogue: O / l -> bf16, LSE
     if (alive) {
+      float* slot = xch + (n_kv & 1) * 256;
+      slot[half * 128 + row] = l;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      l += slot[(half ^ 1) * 128 + row];
       bool ok = mbar_wait(o_done, 0, abort_flag, p.status, 701);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
@@ -319,7 +334,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  (((size_t)b * p.o_rows_per_peer + lrow) * p.o_heads_total + p.o_head_off + hq) * D;
         }
 #pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
+        for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
           uint32_t v[32];
           tmem_ld32(t_lane + O_COL + c, v);
           tmem_wait_ld();
@@ -335,10 +350,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
           }
         }
-        if (row_valid)
+        if (row_valid && half == 0)
           p.lse[((size_t)b * p.Hq + hq) * p.Tq + qi] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
       }
-    } else if (n_kv == 0 && row_valid) {
+    } else if (n_kv == 0 && row_valid && half == 0) {
       // no visible key at all: zero output, LSE = -inf
       __nv_bfloat16* orow = p.O + (((size_t)b * p.Tq + qi) * p.Hq + hq) * D;
       if (p.o_peers != nullptr) {
