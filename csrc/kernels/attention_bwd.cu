@@ -2,30 +2,37 @@
 // every query tile (of every query head of the GQA group) that can see it, with all five products
 // on tcgen05 tensor cores and every accumulator in tensor memory:
 //
-//   S^T  = K Q^T            (smem x smem)          P^T  = exp2(S^T*c - LSE)         (registers)
-//   dP^T = V dO^T           (smem x smem)          dS^T = P^T o (dP^T - Delta) * scale
-//   dV  += P^T  dO          (tmem x smem)          dK  += dS^T Q      (tmem x smem)
-//   dQ   = dS K             (smem x smem, dS^T staged M-major in shared memory) -> staged in shared memory
-//                           and added to the fp32 dQ buffer by TMA reduce (cp.reduce.async.bulk.tensor .add)
+//   S  = Q K^T              (smem x smem)          P  = exp2(S*c - LSE)             (registers -> smem, bf16)
+//   dP = dO V^T             (smem x smem)          dS = P o (dP - Delta)            (registers -> smem, bf16)
+//   dV += P^T dO            (smem x smem, P read M-major)     dK += dS^T Q  (smem x smem, dS read M-major)
+//   dQ  = dS K              (smem x smem, dS read K-major) -> staged in shared memory and added to the fp32
+//                           dQ buffer by TMA reduce (cp.reduce.async.bulk.tensor .add)
 //
-// Computing the transposed score tile puts K/V rows in tensor-memory lanes, so P^T and dS^T feed the
-// dV / dK products directly as tensor-memory A operands and dK / dV never leave tensor memory until
-// the sweep ends.  dK/dV can be written as bf16 or accumulated into fp32 buffers (the ring calls the
-// kernel once per query shard and sums contributions, like the reference's travelling fp32
-// accumulator, context_parallel/ContextParallelBackward.h:151-158,546-627).  P is recomputed from the
-// merged LSE (context_parallel/AttentionBackward.cu:446).  Masking is on global positions, as in the
-// forward.
+// Query rows sit in tensor-memory lanes, so LSE, Delta and the query position are per-thread scalars and
+// the inner loop touches no shared-memory vectors.  The bf16 P and dS tiles are written once to shared
+// memory in the 128-byte-swizzled layout that serves, unchanged, as the M-major A operand of the dV / dK
+// products and as the K-major A operand of the dQ product.  dK / dV stay in tensor memory for the whole
+// sweep and are written as bf16, accumulated into fp32 buffers, or (fused ring) added to their owners'
+// accumulators over NVLink (the ring calls the kernel once per query shard and sums contributions, like
+// the reference's travelling fp32 accumulator, context_parallel/ContextParallelBackward.h:151-158,546-627).
+// dS is formed without the softmax scale; dK is scaled in the final epilogue and dQ in the drain warps.
+// P is recomputed from the merged LSE (context_parallel/AttentionBackward.cu:446).  Masking is on global
+// positions, as in the forward.
 //
 // Replaces mem_efficient_bwd_unified_kernel_exp11 (context_parallel/AttentionBackward.cu:300-541) and
 // gqa_fused_rope_bwd_dQ / _dKdV (context_parallel/GQA_fused_bwd_sm103_cp.cu:135-565).
 //
-// Warp roles (448 threads): 0 = TMA loader, 1 = MMA issuer, 2..9 = softmax-gradient warps (two threads per K/V
-// row, 64 query columns each, so every scheduler has two such warps to hide tensor-memory and MUFU latency),
+// Warp roles (448 threads): 0 = TMA loader, 1 = MMA issuer, 2..9 = softmax-gradient warps (two threads per query
+// row, 64 key columns each, so every scheduler has two such warps to hide tensor-memory and MUFU latency),
 // 10..13 = dQ drain warps (thread = query row).
 #include "common.cuh"
 #include "host_utils.h"
 
+#include <stdlib.h>
+
 namespace cpb {
+
+static __device__ long long g_bwd_prof[16];
 
 constexpr int FB_T = 128;            // tile edge (queries and keys)
 constexpr int FB_THREADS = 448;
@@ -47,6 +54,8 @@ struct BwdParams {
   const uint64_t* route_k;
   const uint64_t* route_v;
   int route_rows, route_tl;
+  int debug_skip_dq;        // diagnostic: do not add dQ tiles to global memory (timing experiments only)
+  long long* debug_prof;    // diagnostic: CTA (0,0,0) writes the MMA thread's cycle breakdown here (6 counters)
   int* status;
 };
 
@@ -58,7 +67,8 @@ struct BwdSmem {
   static constexpr int V_OFF = TILE;
   static constexpr int Q_OFF = 2 * TILE;
   static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
-  static constexpr int DS_OFF = DO_OFF + STAGES * TILE;           // dS^T: 128 x 128 bf16, M-major
+  static constexpr int PS_OFF = DO_OFF + STAGES * TILE;           // P : 128 queries x 128 keys bf16, 128B-swizzled
+  static constexpr int DS_OFF = PS_OFF + FB_T * FB_T * 2;         // dS: same layout
   static constexpr int DQS_OFF = DS_OFF + FB_T * FB_T * 2;        // dQ staging: 2 boxes of 128 rows x 32 fp32, 128B-swizzled
   static constexpr int VEC_OFF = DQS_OFF + 2 * FB_T * 128;        // per stage: lse2[128], delta[128], qpos[128]
   static constexpr int BAR_OFF = VEC_OFF + STAGES * 3 * 512;
@@ -81,8 +91,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   using L = BwdSmem<D>;
   constexpr int ST = L::STAGES;
   constexpr int DH = D / 64;
-  constexpr uint32_t ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
-  constexpr uint32_t DQ_COL = (D == 64) ? 384 : 0;           // D=128: dQ reuses the S^T columns
+  constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + D;
+  constexpr uint32_t DQ_COL = (D == 64) ? 384 : 0;           // D=128: dQ reuses the S columns
   constexpr bool DQ_ALIAS = (D != 64);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -166,57 +176,68 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_it > 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(FB_T, FB_T, false, false);     // S^T, dP^T
-      constexpr uint32_t idesc_acc = make_idesc_bf16(FB_T, D, false, true);        // dV, dK: A in tmem, B N-major
-      constexpr uint32_t idesc_dq = make_idesc_bf16(FB_T, D, true, true);          // dQ: A M-major smem, B N-major
-      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF), sDS = smem_u32(smem + L::DS_OFF);
+      constexpr uint32_t idesc_s = make_idesc_bf16(FB_T, FB_T, false, false);     // S, dP
+      constexpr uint32_t idesc_acc = make_idesc_bf16(FB_T, D, true, true);         // dV, dK: A M-major smem, B N-major
+      constexpr uint32_t idesc_dq = make_idesc_bf16(FB_T, D, false, true);         // dQ: A K-major smem, B N-major
+      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
+      const uint32_t sP = smem_u32(smem + L::PS_OFF), sDS = smem_u32(smem + L::DS_OFF);
       if (mbar_wait(kv_full, 0, abort_flag, p.status, 900)) {
+        long long prof[6] = {0, 0, 0, 0, 0, 0};
+        const bool do_prof = p.debug_prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
         for (int i = 0; i < n_it; ++i) {
           const int st = i % ST;
           const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE), sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
+          long long t0 = do_prof ? clock64() : 0;
           if (!mbar_wait(&q_full[st], (i / ST) & 1, abort_flag, p.status, 901)) break;
+          if (do_prof) { long long t = clock64(); prof[0] += t - t0; t0 = t; }
           if (DQ_ALIAS && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 902)) break;
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
+          for (int k = 0; k < D / 16; ++k) {       // S = Q K^T
             const uint32_t off = (k / 4) * (FB_T * 128) + (k % 4) * 32;
-            umma_ss(tmem_base + ST_COL, sdesc_kmajor(sK + off), sdesc_kmajor(sQ + off), idesc_s, k != 0);
+            umma_ss(tmem_base + S_COL, sdesc_kmajor(sQ + off), sdesc_kmajor(sK + off), idesc_s, k != 0);
           }
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
+          for (int k = 0; k < D / 16; ++k) {       // dP = dO V^T
             const uint32_t off = (k / 4) * (FB_T * 128) + (k % 4) * 32;
-            umma_ss(tmem_base + DPT_COL, sdesc_kmajor(sV + off), sdesc_kmajor(sDO + off), idesc_s, k != 0);
+            umma_ss(tmem_base + DP_COL, sdesc_kmajor(sDO + off), sdesc_kmajor(sV + off), idesc_s, k != 0);
           }
           umma_commit(s_full);
+          if (do_prof) { long long t = clock64(); prof[1] += t - t0; t0 = t; }
           if (!mbar_wait(p_full, i & 1, abort_flag, p.status, 903)) break;
+          if (do_prof) { long long t = clock64(); prof[2] += t - t0; t0 = t; }
           if (!DQ_ALIAS && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 904)) break;
+          if (do_prof) { long long t = clock64(); prof[3] += t - t0; t0 = t; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < FB_T / 16; ++k)      // dV += P^T dO : contraction over the 128 queries
-            umma_ts(tmem_base + DV_COL, tmem_base + ST_COL + (k >> 2) * 64 + (k & 3) * 8, make_sdesc(sDO + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
+          for (int k = 0; k < FB_T / 16; ++k)      // dV += P^T dO : contraction over the 128 queries (tile rows)
+            umma_ss(tmem_base + DV_COL, make_sdesc(sP + k * 2048, FB_T * 128, 1024), make_sdesc(sDO + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
 #pragma unroll
           for (int k = 0; k < FB_T / 16; ++k)      // dK += dS^T Q
-            umma_ts(tmem_base + DK_COL, tmem_base + DPT_COL + (k >> 2) * 64 + (k & 3) * 8, make_sdesc(sQ + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
+            umma_ss(tmem_base + DK_COL, make_sdesc(sDS + k * 2048, FB_T * 128, 1024), make_sdesc(sQ + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
 #pragma unroll
-          for (int k = 0; k < FB_T / 16; ++k)      // dQ = dS K : contraction over the 128 keys
-            umma_ss(tmem_base + DQ_COL, make_sdesc(sDS + k * 2048, FB_T * 128, 1024), make_sdesc(sK + k * 2048, FB_T * 128, 1024), idesc_dq, k != 0);
+          for (int k = 0; k < FB_T / 16; ++k)      // dQ = dS K : contraction over the 128 keys (tile columns)
+            umma_ss(tmem_base + DQ_COL, sdesc_kmajor(sDS + (k >> 2) * (FB_T * 128) + (k & 3) * 32), make_sdesc(sK + k * 2048, FB_T * 128, 1024), idesc_dq, k != 0);
           umma_commit(&q_empty[st]);
           umma_commit(dq_full);
+          if (do_prof) { long long t = clock64(); prof[4] += t - t0; prof[5] += 1; }
         }
+        if (do_prof) for (int z = 0; z < 6; ++z) p.debug_prof[z] = prof[z];
         umma_commit(acc_done);
       }
     }
   } else if (warp < 10) {
     // ------------------------------------------------------------------ softmax-gradient warps
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;                   // which 64 query columns of the tile this thread owns
+    const int half = (warp - 2) >> 2;                   // which 64 key columns of the tile this thread owns
     const int cbase = half * 64;
-    const int r = quarter * 32 + lane;                  // K/V row inside the tile
-    const int kidx = k0 + r;
+    const int r = quarter * 32 + lane;                  // query row inside the tile (epilogue: K/V row)
+    const int kidx = k0 + r;                            // epilogue only: the K/V row this thread drains
     const bool k_valid = kidx < p.Tk;
-    const int kpos = p.k_off + kidx;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    uint8_t* p_row = smem + L::PS_OFF + half * (FB_T * 128) + r * 128;
     uint8_t* ds_row = smem + L::DS_OFF + half * (FB_T * 128) + r * 128;
+    const int kcol0 = k0 + cbase;                       // key index of this thread's first column
     bool alive = true;
     for (int i = 0; i < n_it && alive; ++i) {
       const int st = i % ST;
@@ -225,56 +246,45 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { alive = false; break; }
       tc_fence_after();
-      const float* lse2 = (const float*)(smem + L::VEC_OFF + st * 1536) + cbase;
-      const float* delta = lse2 + 128;
-      const int* qpos = (const int*)(lse2 + 256);
-      const bool need_mask = p.causal && (p.k_off + k0 + FB_T - 1 > qpos[0]);
+      const float* vec = (const float*)(smem + L::VEC_OFF + st * 1536);
+      const float lse2_r = vec[r], delta_r = vec[128 + r];
+      const int qpos_r = ((const int*)vec)[256 + r], qpos_min = ((const int*)vec)[256];
+      // slow path only for tiles that touch the causal diagonal or the end of the key sequence
+      const bool need_mask = (k0 + FB_T > p.Tk) || (p.causal && (p.k_off + k0 + FB_T - 1 > qpos_min));
+      const int kmax = min(p.causal ? qpos_r - p.k_off : 0x7fffffff, p.Tk - 1) - kcol0;   // last visible column of my span
       // 4 chunks of 16 columns; the tensor-memory loads of chunk ch+1 are in flight while chunk ch is processed.
-      // P^T / dS^T (bf16, two per column) go back into the first 32 columns of this thread's own 64-column
-      // span, always behind the columns already consumed.
       uint32_t sv[4][16], dpv[4][16];
-      tmem_ld16(t_lane + ST_COL + cbase, sv[0]);
-      tmem_ld16(t_lane + DPT_COL + cbase, dpv[0]);
+      tmem_ld16(t_lane + S_COL + cbase, sv[0]);
+      tmem_ld16(t_lane + DP_COL + cbase, dpv[0]);
       tmem_wait_ld();
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         if (ch < 3) {
-          tmem_ld16(t_lane + ST_COL + cbase + 16 * (ch + 1), sv[ch + 1]);
-          tmem_ld16(t_lane + DPT_COL + cbase + 16 * (ch + 1), dpv[ch + 1]);
+          tmem_ld16(t_lane + S_COL + cbase + 16 * (ch + 1), sv[ch + 1]);
+          tmem_ld16(t_lane + DP_COL + cbase + 16 * (ch + 1), dpv[ch + 1]);
         }
         uint32_t pk[8], dk_[8];
 #pragma unroll
-        for (int j = 0; j < 16; j += 4) {
-          const float4 l4 = *(const float4*)(lse2 + ch * 16 + j);
-          const float4 d4 = *(const float4*)(delta + ch * 16 + j);
-          float p0 = ex2f(fmaf(__uint_as_float(sv[ch][j]), p.scale_log2, -l4.x));
-          float p1 = ex2f(fmaf(__uint_as_float(sv[ch][j + 1]), p.scale_log2, -l4.y));
-          float p2 = ex2f(fmaf(__uint_as_float(sv[ch][j + 2]), p.scale_log2, -l4.z));
-          float p3 = ex2f(fmaf(__uint_as_float(sv[ch][j + 3]), p.scale_log2, -l4.w));
-          if (!k_valid) { p0 = p1 = p2 = p3 = 0.f; }
+        for (int j = 0; j < 16; j += 2) {
+          float p0 = ex2f(fmaf(__uint_as_float(sv[ch][j]), p.scale_log2, -lse2_r));
+          float p1 = ex2f(fmaf(__uint_as_float(sv[ch][j + 1]), p.scale_log2, -lse2_r));
           if (need_mask) {
-            const int4 q4 = *(const int4*)(qpos + ch * 16 + j);
-            if (kpos > q4.x) p0 = 0.f;
-            if (kpos > q4.y) p1 = 0.f;
-            if (kpos > q4.z) p2 = 0.f;
-            if (kpos > q4.w) p3 = 0.f;
+            if (ch * 16 + j > kmax) p0 = 0.f;
+            if (ch * 16 + j + 1 > kmax) p1 = 0.f;
           }
-          const float e0 = p0 * (__uint_as_float(dpv[ch][j]) - d4.x) * p.scale;
-          const float e1 = p1 * (__uint_as_float(dpv[ch][j + 1]) - d4.y) * p.scale;
-          const float e2 = p2 * (__uint_as_float(dpv[ch][j + 2]) - d4.z) * p.scale;
-          const float e3 = p3 * (__uint_as_float(dpv[ch][j + 3]) - d4.w) * p.scale;
-          pk[j >> 1] = pack_bf16(p0, p1); pk[(j >> 1) + 1] = pack_bf16(p2, p3);
-          dk_[j >> 1] = pack_bf16(e0, e1); dk_[(j >> 1) + 1] = pack_bf16(e2, e3);
+          const float e0 = p0 * (__uint_as_float(dpv[ch][j]) - delta_r);
+          const float e1 = p1 * (__uint_as_float(dpv[ch][j + 1]) - delta_r);
+          pk[j >> 1] = pack_bf16(p0, p1);
+          dk_[j >> 1] = pack_bf16(e0, e1);
         }
-        tmem_st8(t_lane + ST_COL + cbase + ch * 8, pk);
-        tmem_st8(t_lane + DPT_COL + cbase + ch * 8, dk_);
-        // dS^T row r -> shared memory, M-major 128B-swizzled: 16-byte chunk (q % 64) / 8 of this thread's
-        // 64-query group goes to chunk position (chunk ^ (r & 7)).
+        // row r of P and dS -> shared memory, 128B-swizzled: 16-byte chunk (col % 64) / 8 of this thread's 64-key
+        // group goes to chunk position (chunk ^ (r & 7)).
+        *(uint4*)(p_row + (((2 * ch) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *(uint4*)(p_row + (((2 * ch + 1) ^ (r & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         *(uint4*)(ds_row + (((2 * ch) ^ (r & 7)) << 4)) = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
         *(uint4*)(ds_row + (((2 * ch + 1) ^ (r & 7)) << 4)) = make_uint4(dk_[4], dk_[5], dk_[6], dk_[7]);
         if (ch < 3) tmem_wait_ld();
       }
-      tmem_wait_st();
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
@@ -297,11 +307,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int which = half; which <= half; ++which) {          // first warp group drains dK, second dV
           const uint32_t col = which ? DV_COL : DK_COL;
           void* base = which ? p.dv : p.dk;
+          const float osc = which ? 1.f : p.scale;          // dS^T was accumulated without the softmax scale
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
             uint32_t v[32];
             tmem_ld32(t_lane + col + c, v);
             tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * osc);
             if (k_valid) {
               if (p.dkv_f32_accumulate == 2) {
                 const int ch = kidx / p.route_rows, lrow = kidx % p.route_rows;
@@ -362,13 +375,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_wait_ld();
           uint8_t* rowp = stage + bx * (FB_T * 128) + r * 128;
 #pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4)
-            *(uint4*)(rowp + ((c4 ^ (r & 7)) << 4)) = make_uint4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+          for (int c4 = 0; c4 < 8; ++c4)        // dS was formed without the softmax scale: apply it here
+            *(float4*)(rowp + ((c4 ^ (r & 7)) << 4)) = make_float4(__uint_as_float(v[4 * c4]) * p.scale, __uint_as_float(v[4 * c4 + 1]) * p.scale,
+                                                                   __uint_as_float(v[4 * c4 + 2]) * p.scale, __uint_as_float(v[4 * c4 + 3]) * p.scale);
         }
         if (rnd == D / 64 - 1) { tc_fence_before(); mbar_arrive(dq_empty); }     // tensor-memory dQ is free again
         fence_proxy_async_smem();
         asm volatile("bar.sync 5, 128;" ::: "memory");
-        if (issuer) {
+        if (issuer && !p.debug_skip_dq) {
 #pragma unroll
           for (int bx = 0; bx < 2; ++bx)
             asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
@@ -481,6 +495,16 @@ extern "C" int cpb_flash_bwd(const void* q, const void* k, const void* v, const 
   p.lse2 = lse2; p.delta = delta; p.q_pos = q_pos; p.dq = dq; p.dk = dk; p.dv = dv;
   p.dkv_f32_accumulate = dkv_f32_accumulate; p.status = status;
   p.route_k = route_k; p.route_v = route_v; p.route_rows = route_rows; p.route_tl = route_tl;
+  {
+    const char* e = getenv("CPB_BWD_SKIP_DQ");
+    p.debug_skip_dq = (e != nullptr && e[0] == '1');
+    p.debug_prof = nullptr;
+    const char* pe = getenv("CPB_BWD_PROF");
+    if (pe != nullptr && pe[0] == '1') {
+      void* sym = nullptr;
+      if (cudaGetSymbolAddress(&sym, g_bwd_prof) == cudaSuccess) p.debug_prof = (long long*)sym;
+    }
+  }
   if (dkv_f32_accumulate == 2 && (route_k == nullptr || route_v == nullptr || route_rows <= 0))
     return set_error(CPB_ERR_ARG, "flash_bwd: routed dK/dV needs route tables");
   dim3 grid((Tk + FB_T - 1) / FB_T, Hkv, B);
@@ -492,6 +516,13 @@ extern "C" int cpb_flash_bwd(const void* q, const void* k, const void* v, const 
     static bool cfg = false;
     if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::TOTAL)); cfg = true; }
     flash_bwd_kernel<128><<<grid, FB_THREADS, BwdSmem<128>::TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);
+  }
+  if (p.debug_prof != nullptr) {
+    long long h[6];
+    cudaStreamSynchronize(stream);
+    if (cudaMemcpy(h, p.debug_prof, sizeof(h), cudaMemcpyDeviceToHost) == cudaSuccess && h[5] > 0)
+      fprintf(stderr, "[flash_bwd prof] iters=%lld MMA-thread cycles per tile: wait_q=%lld issue_scores=%lld wait_p=%lld wait_dq=%lld issue_grads=%lld\n",
+              h[5], h[0] / h[5], h[1] / h[5], h[2] / h[5], h[3] / h[5], h[4] / h[5]);
   }
   return check_launch("flash_bwd");
 }

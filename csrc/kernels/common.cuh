@@ -72,18 +72,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint: the hardware parks the thread until the phase completes or the hint
+// (nanoseconds) runs out, so a waiting warp does not burn issue slots and shared-memory bandwidth that the
+// working warps of the same SM partition need.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  `abort_flag` lives in shared memory; once any waiter of the CTA has timed out
-// every later wait returns at once so the kernel drains in bounded time.
+// every later wait returns at once so the kernel drains in bounded time.  Worst case: CPB_WAIT_SPINS
+// suspensions of CPB_WAIT_HINT_NS each (about 2 s).
 #ifndef CPB_WAIT_SPINS
-#define CPB_WAIT_SPINS (1u << 22)
+#define CPB_WAIT_SPINS (100000u)
+#endif
+#ifndef CPB_WAIT_HINT_NS
+#define CPB_WAIT_HINT_NS (20000u)
 #endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int site) {
   if (mbar_try_wait(bar, parity)) return true;
   for (uint32_t it = 0; it < CPB_WAIT_SPINS; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, CPB_WAIT_HINT_NS)) return true;
     if (*abort_flag) return false;
-    if (it > 4096) __nanosleep(64);
   }
   *abort_flag = 1;
   report(status, ST_TIMEOUT_MBAR, site, (int)parity);
