@@ -68,9 +68,11 @@ struct BwdSmem {
   static constexpr int Q_OFF = 2 * TILE;
   static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
   static constexpr int PS_OFF = DO_OFF + STAGES * TILE;           // P : 128 queries x 128 keys bf16, 128B-swizzled
+  static constexpr int DS_BUFS = (D == 64) ? 2 : 1;               // head_dim 64: dS double-buffered (pipelined issue order)
   static constexpr int DS_OFF = PS_OFF + FB_T * FB_T * 2;         // dS: same layout
-  static constexpr int DQS_OFF = DS_OFF + FB_T * FB_T * 2;        // dQ staging: 2 boxes of 128 rows x 32 fp32, 128B-swizzled
-  static constexpr int VEC_OFF = DQS_OFF + 2 * FB_T * 128;        // per stage: lse2[128], delta[128], qpos[128]
+  static constexpr int DQS_OFF = DS_OFF + DS_BUFS * FB_T * FB_T * 2;   // dQ staging: boxes of 128 rows x 32 fp32, 128B-swizzled
+  static constexpr int DQ_BOXES = (D == 64) ? 1 : 2;              // boxes staged per TMA-reduce round
+  static constexpr int VEC_OFF = DQS_OFF + DQ_BOXES * FB_T * 128;        // per stage: lse2[128], delta[128], qpos[128]
   static constexpr int BAR_OFF = VEC_OFF + STAGES * 3 * 512;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
@@ -94,6 +96,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + D;
   constexpr uint32_t DQ_COL = (D == 64) ? 384 : 0;           // D=128: dQ reuses the S columns
   constexpr bool DQ_ALIAS = (D != 64);
+  constexpr bool OVERLAP = (D == 64);                         // pipelined issue order (see the MMA issuer)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + L::BAR_OFF);
@@ -105,7 +108,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* dq_full = bars + 7;
   uint64_t* dq_empty = bars + 8;
   uint64_t* acc_done = bars + 9;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+  uint64_t* ds_empty = bars + 10;     // [2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* qt_start_s = (int*)(tmem_slot + 2);
 
@@ -119,6 +123,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     mbar_init(s_full, 1); mbar_init(p_full, 256); mbar_init(dq_full, 1); mbar_init(dq_empty, 128); mbar_init(acc_done, 1);
+    mbar_init(&ds_empty[0], 1); mbar_init(&ds_empty[1], 1);
     *abort_flag = 0;
     *qt_start_s = num_q_tiles;
     fence_mbar_init();
@@ -184,14 +189,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (mbar_wait(kv_full, 0, abort_flag, p.status, 900)) {
         long long prof[6] = {0, 0, 0, 0, 0, 0};
         const bool do_prof = p.debug_prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-        for (int i = 0; i < n_it; ++i) {
-          const int st = i % ST;
-          const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE), sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
-          long long t0 = do_prof ? clock64() : 0;
-          if (!mbar_wait(&q_full[st], (i / ST) & 1, abort_flag, p.status, 901)) break;
-          if (do_prof) { long long t = clock64(); prof[0] += t - t0; t0 = t; }
-          if (DQ_ALIAS && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 902)) break;
-          tc_fence_after();
+        auto issue_scores = [&](uint32_t sQ, uint32_t sDO) {
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {       // S = Q K^T
             const uint32_t off = (k / 4) * (FB_T * 128) + (k % 4) * 32;
@@ -203,24 +201,82 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             umma_ss(tmem_base + DP_COL, sdesc_kmajor(sDO + off), sdesc_kmajor(sV + off), idesc_s, k != 0);
           }
           umma_commit(s_full);
-          if (do_prof) { long long t = clock64(); prof[1] += t - t0; t0 = t; }
-          if (!mbar_wait(p_full, i & 1, abort_flag, p.status, 903)) break;
-          if (do_prof) { long long t = clock64(); prof[2] += t - t0; t0 = t; }
-          if (!DQ_ALIAS && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 904)) break;
-          if (do_prof) { long long t = clock64(); prof[3] += t - t0; t0 = t; }
-          tc_fence_after();
+        };
+        auto issue_dv = [&](uint32_t sDO, int i) {       // dV += P^T dO : contraction over the 128 queries (tile rows)
 #pragma unroll
-          for (int k = 0; k < FB_T / 16; ++k)      // dV += P^T dO : contraction over the 128 queries (tile rows)
+          for (int k = 0; k < FB_T / 16; ++k)
             umma_ss(tmem_base + DV_COL, make_sdesc(sP + k * 2048, FB_T * 128, 1024), make_sdesc(sDO + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
+        };
+        auto issue_dk = [&](uint32_t sQ, uint32_t sDSi, int i) {   // dK += dS^T Q
 #pragma unroll
-          for (int k = 0; k < FB_T / 16; ++k)      // dK += dS^T Q
-            umma_ss(tmem_base + DK_COL, make_sdesc(sDS + k * 2048, FB_T * 128, 1024), make_sdesc(sQ + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
+          for (int k = 0; k < FB_T / 16; ++k)
+            umma_ss(tmem_base + DK_COL, make_sdesc(sDSi + k * 2048, FB_T * 128, 1024), make_sdesc(sQ + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
+        };
+        auto issue_dq = [&](uint32_t sDSi) {             // dQ = dS K : contraction over the 128 keys (tile columns)
 #pragma unroll
-          for (int k = 0; k < FB_T / 16; ++k)      // dQ = dS K : contraction over the 128 keys (tile columns)
-            umma_ss(tmem_base + DQ_COL, sdesc_kmajor(sDS + (k >> 2) * (FB_T * 128) + (k & 3) * 32), make_sdesc(sK + k * 2048, FB_T * 128, 1024), idesc_dq, k != 0);
-          umma_commit(&q_empty[st]);
-          umma_commit(dq_full);
-          if (do_prof) { long long t = clock64(); prof[4] += t - t0; prof[5] += 1; }
+          for (int k = 0; k < FB_T / 16; ++k)
+            umma_ss(tmem_base + DQ_COL, sdesc_kmajor(sDSi + (k >> 2) * (FB_T * 128) + (k & 3) * 32), make_sdesc(sK + k * 2048, FB_T * 128, 1024), idesc_dq, k != 0);
+        };
+        if (OVERLAP) {
+          // Pipelined order (head_dim 64).  When the softmax-gradient warps finish tile i the issuer queues
+          //   dV(i) | S(i+1), dP(i+1) | dK(i), dQ(i)
+          // so the warps start on tile i+1 as soon as its score products are done while dK(i) and dQ(i), which
+          // read the double-buffered dS tile, still run on the tensor cores.  P is single-buffered: dV(i) is
+          // ordered before S(i+1), whose completion is what lets the warps overwrite P.
+          bool ok = mbar_wait(&q_full[0], 0, abort_flag, p.status, 901);
+          if (ok) {
+            tc_fence_after();
+            issue_scores(smem_u32(smem + L::Q_OFF), smem_u32(smem + L::DO_OFF));
+          }
+          for (int i = 0; ok && i < n_it; ++i) {
+            const int st = i % ST;
+            const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE), sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
+            const uint32_t sDSi = sDS + (i & 1) * (FB_T * FB_T * 2);
+            long long t0 = do_prof ? clock64() : 0;
+            if (!mbar_wait(p_full, i & 1, abort_flag, p.status, 903)) break;
+            if (do_prof) { long long t = clock64(); prof[2] += t - t0; t0 = t; }
+            tc_fence_after();
+            issue_dv(sDO, i);
+            if (i + 1 < n_it) {
+              const int sn = (i + 1) % ST;
+              if (!mbar_wait(&q_full[sn], ((i + 1) / ST) & 1, abort_flag, p.status, 901)) break;
+              tc_fence_after();
+              issue_scores(smem_u32(smem + L::Q_OFF + sn * L::TILE), smem_u32(smem + L::DO_OFF + sn * L::TILE));
+            }
+            if (do_prof) { long long t = clock64(); prof[1] += t - t0; t0 = t; }
+            issue_dk(sQ, sDSi, i);
+            if (i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 904)) break;
+            if (do_prof) { long long t = clock64(); prof[3] += t - t0; t0 = t; }
+            tc_fence_after();
+            issue_dq(sDSi);
+            umma_commit(&q_empty[st]);
+            umma_commit(&ds_empty[i & 1]);
+            umma_commit(dq_full);
+            if (do_prof) { long long t = clock64(); prof[4] += t - t0; prof[5] += 1; }
+          }
+        } else {
+          for (int i = 0; i < n_it; ++i) {
+            const int st = i % ST;
+            const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE), sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
+            long long t0 = do_prof ? clock64() : 0;
+            if (!mbar_wait(&q_full[st], (i / ST) & 1, abort_flag, p.status, 901)) break;
+            if (do_prof) { long long t = clock64(); prof[0] += t - t0; t0 = t; }
+            if (DQ_ALIAS && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 902)) break;
+            tc_fence_after();
+            issue_scores(sQ, sDO);
+            if (do_prof) { long long t = clock64(); prof[1] += t - t0; t0 = t; }
+            if (!mbar_wait(p_full, i & 1, abort_flag, p.status, 903)) break;
+            if (do_prof) { long long t = clock64(); prof[2] += t - t0; t0 = t; }
+            if (!DQ_ALIAS && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 904)) break;
+            if (do_prof) { long long t = clock64(); prof[3] += t - t0; t0 = t; }
+            tc_fence_after();
+            issue_dv(sDO, i);
+            issue_dk(sQ, sDS, i);
+            issue_dq(sDS);
+            umma_commit(&q_empty[st]);
+            umma_commit(dq_full);
+            if (do_prof) { long long t = clock64(); prof[4] += t - t0; prof[5] += 1; }
+          }
         }
         if (do_prof) for (int z = 0; z < 6; ++z) p.debug_prof[z] = prof[z];
         umma_commit(acc_done);
@@ -236,7 +292,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const bool k_valid = kidx < p.Tk;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
     uint8_t* p_row = smem + L::PS_OFF + half * (FB_T * 128) + r * 128;
-    uint8_t* ds_row = smem + L::DS_OFF + half * (FB_T * 128) + r * 128;
+    uint8_t* ds_row0 = smem + L::DS_OFF + half * (FB_T * 128) + r * 128;
     const int kcol0 = k0 + cbase;                       // key index of this thread's first column
     bool alive = true;
     for (int i = 0; i < n_it && alive; ++i) {
@@ -253,6 +309,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const bool need_mask = (k0 + FB_T > p.Tk) || (p.causal && (p.k_off + k0 + FB_T - 1 > qpos_min));
       const int kmax = min(p.causal ? qpos_r - p.k_off : 0x7fffffff, p.Tk - 1) - kcol0;   // last visible column of my span
       // 4 chunks of 16 columns; the tensor-memory loads of chunk ch+1 are in flight while chunk ch is processed.
+      uint8_t* ds_row = ds_row0 + (OVERLAP ? (i & 1) * (FB_T * FB_T * 2) : 0);
+      if (OVERLAP) {
+        // this parity's dS buffer was last read by dK/dQ of tile i-2
+        bool ok2 = mbar_wait(&ds_empty[i & 1], ((i >> 1) & 1) ^ 1, abort_flag, p.status, 1003);
+        ok2 = __all_sync(0xffffffffu, ok2);
+        if (!ok2) { alive = false; break; }
+      }
       uint32_t sv[4][16], dpv[4][16];
       tmem_ld16(t_lane + S_COL + cbase, sv[0]);
       tmem_ld16(t_lane + DP_COL + cbase, dpv[0]);
@@ -366,12 +429,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       const int hq = hkv * G + i / n_qt;
       const int q0 = (qt_start + i % n_qt) * FB_T;
+      constexpr int NB = L::DQ_BOXES;
 #pragma unroll 1
-      for (int rnd = 0; rnd < D / 64; ++rnd) {
+      for (int rnd = 0; rnd < D / (32 * NB); ++rnd) {   // NB boxes of 128 x 32 fp32 per round through the staging tile
 #pragma unroll
-        for (int bx = 0; bx < 2; ++bx) {
+        for (int bx = 0; bx < NB; ++bx) {
           uint32_t v[32];
-          tmem_ld32(t_lane + DQ_COL + rnd * 64 + bx * 32, v);
+          tmem_ld32(t_lane + DQ_COL + (rnd * NB + bx) * 32, v);
           tmem_wait_ld();
           uint8_t* rowp = stage + bx * (FB_T * 128) + r * 128;
 #pragma unroll
@@ -379,14 +443,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             *(float4*)(rowp + ((c4 ^ (r & 7)) << 4)) = make_float4(__uint_as_float(v[4 * c4]) * p.scale, __uint_as_float(v[4 * c4 + 1]) * p.scale,
                                                                    __uint_as_float(v[4 * c4 + 2]) * p.scale, __uint_as_float(v[4 * c4 + 3]) * p.scale);
         }
-        if (rnd == D / 64 - 1) { tc_fence_before(); mbar_arrive(dq_empty); }     // tensor-memory dQ is free again
+        if (rnd == D / (32 * NB) - 1) { tc_fence_before(); mbar_arrive(dq_empty); }   // tensor-memory dQ is free again
         fence_proxy_async_smem();
         asm volatile("bar.sync 5, 128;" ::: "memory");
         if (issuer && !p.debug_skip_dq) {
 #pragma unroll
-          for (int bx = 0; bx < 2; ++bx)
+          for (int bx = 0; bx < NB; ++bx)
             asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                         ::"l"((uint64_t)&tmDQ), "r"(smem_u32(stage + bx * (FB_T * 128))), "r"(rnd * 64 + bx * 32), "r"(hq), "r"(q0), "r"(b)
+                         ::"l"((uint64_t)&tmDQ), "r"(smem_u32(stage + bx * (FB_T * 128))), "r"((rnd * NB + bx) * 32), "r"(hq), "r"(q0), "r"(b)
                          : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");

@@ -96,7 +96,10 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
 #endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int site) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // short waits (the common case inside a pipelined kernel) spin; long waits are parked by the hardware
+#pragma unroll 1
+  for (int it = 0; it < 256; ++it)
+    if (mbar_try_wait(bar, parity)) return true;
   for (uint32_t it = 0; it < CPB_WAIT_SPINS; ++it) {
     if (mbar_try_wait_hint(bar, parity, CPB_WAIT_HINT_NS)) return true;
     if (*abort_flag) return false;
