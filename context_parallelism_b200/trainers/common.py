@@ -65,6 +65,7 @@ def train(cfg: Config, eng: TrainEngine, impl: str, csv_header: str,
     log_path = os.path.join(cfg.log_dir, f"{cfg.ckpt_prefix}_run{run}_log.csv")
     csv = M.CsvLog(log_path, csv_header, resumed=resuming, resume_note=f"from step {start_step}")
     if rank == 0 and not cfg.mem_probe:
+        os.makedirs(cfg.log_dir, exist_ok=True)
         with open(os.path.join(cfg.log_dir, f"{cfg.ckpt_prefix}_run{run}_config.txt"), "w") as f:
             f.write(cfg.describe() + "\n")
     timers = M.PhaseTimers(dev)

@@ -1,0 +1,118 @@
+"""The two trainers end to end on CPU (tiny models): training with checkpoints and auto-resume, CSV/log output,
+per-position perplexity evaluation that is invariant to the CP degree and mode, the resident LongRoPE
+evaluator protocol, CREAM relabelling, dump modes, memory probe."""
+import csv
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TINY = {"CP_N_EMBD": "32", "CP_N_LAYER": "2", "CP_N_HEAD": "4", "CP_N_KVHEAD": "2", "CP_HEAD_DIM": "8", "CP_FFN": "64",
+        "CP_VOCAB": "97", "CP_T": "64", "CP_B": "2", "CP_GLOBAL_BATCH": "128", "CP_WARMUP": "2", "CP_SYNTHETIC": "1",
+        "CP_VAL_FREQ": "4", "CP_VAL_STEPS": "1", "OMP_NUM_THREADS": "1"}
+_PORT = [29800]
+
+
+def run(module, env, nproc=1, stdin=None, timeout=600):
+    e = {k: v for k, v in os.environ.items() if not k.startswith(("CP_", "YARN_"))}
+    e.update(TINY)
+    e.update({k: str(v) for k, v in env.items()})
+    e["PYTHONPATH"] = ROOT
+    if nproc == 1:
+        cmd = [sys.executable, "-m", module]
+    else:
+        _PORT[0] += 1
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+               "--master-port", str(_PORT[0] + os.getpid() % 150), "-m", module]
+    r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=timeout, input=stdin, cwd=ROOT)
+    assert r.returncode == 0, f"{module} failed\n{r.stdout[-3000:]}\n{r.stderr[-3000:]}"
+    return r.stdout
+
+
+def test_llama_train_checkpoint_resume(tmp_path):
+    env = {"CP_CKPT_DIR": tmp_path / "ck", "CP_LOG_DIR": tmp_path, "CP_CKPT_FREQ": "3", "CP_MAX_STEPS": "6", "CP_CKPT": "1"}
+    out = run("context_parallelism_b200.trainers.llama_cp", dict(env, CP_MAX_STEPS="3"))
+    assert "step     2" in out
+    run_dir = tmp_path / "ck" / "blumodelcp_run0"
+    assert (run_dir / "blumodelcp_run0_step_3.ckpt").exists()
+    out2 = run("context_parallelism_b200.trainers.llama_cp", env)              # auto-resume run 0 at step 3
+    assert "[resume] run 0 from step 3" in out2 and "step     5" in out2 and "step     2 " not in out2
+    rows = list(csv.reader(open(tmp_path / "blumodelcp_run0_log.csv")))
+    assert rows[0][:4] == ["step", "loss", "val_loss", "lr"]
+    assert any(r and r[0].startswith("# resumed") for r in rows)
+    steps = [int(r[0]) for r in rows[1:] if r and r[0].isdigit()]
+    assert steps == [0, 1, 2, 3, 4, 5]
+    # an uninterrupted run gives the same final loss as the resumed one
+    env3 = dict(env, CP_CKPT_DIR=tmp_path / "ck2", CP_LOG_DIR=tmp_path / "l2")
+    run("context_parallelism_b200.trainers.llama_cp", env3)
+    rows3 = [r for r in csv.reader(open(tmp_path / "l2" / "blumodelcp_run0_log.csv")) if r and r[0].isdigit()]
+    rows1 = [r for r in rows if r and r[0].isdigit()]
+    assert abs(float(rows3[-1][1]) - float(rows1[-1][1])) < 1e-5
+    out4 = run("context_parallelism_b200.trainers.llama_cp", dict(env, CP_CKPT_NEW_RUN="1", CP_MAX_STEPS="1"))
+    assert (tmp_path / "ck" / "blumodelcp_run1").exists()
+
+
+def test_eval_ppl_is_cp_invariant(tmp_path):
+    base = {"CP_CKPT": "0", "CP_EVAL_PPL": "1", "CP_EVAL_WINDOWS": "2", "CP_LOG_DIR": tmp_path}
+    outs = {}
+    for tag, nproc, mode in (("cp1", 1, "ring"), ("ring2", 2, "ring"), ("uly2", 2, "ulysses")):
+        p = tmp_path / f"ppl_{tag}.csv"
+        run("context_parallelism_b200.trainers.llama_cp", dict(base, CP_EVAL_OUT=p, CP_ATTN_MODE=mode, CP_ROTATOR="p2p"), nproc)
+        outs[tag] = [float(r[2]) for r in list(csv.reader(open(p)))[1:]]
+    assert len(outs["cp1"]) == 64
+    for tag in ("ring2", "uly2"):
+        for a, b in zip(outs["cp1"], outs[tag]):
+            assert abs(a - b) <= 1e-3 * abs(a) + 1e-5
+
+
+def test_longrope_resident_evaluator(tmp_path):
+    good = tmp_path / "good.txt"
+    good.write_text("n_hat=4\ns=2\nsearch_len=64\n" + " ".join(["1.0", "1.5", "2.0", "2.0"]) + "\n")
+    bad = tmp_path / "bad.txt"
+    bad.write_text("2.0 1.0 1.0 1.0\n")                                   # not monotone -> rejected
+    ident = tmp_path / "ident.txt"
+    ident.write_text("1.0 1.0 1.0 1.0\n")
+    stdin = f"{ident}\n{bad}\n{good}\n{ident}\nquit\n"
+    out = run("context_parallelism_b200.trainers.llama_cp", {"CP_CKPT": "0", "CP_LONGROPE_SEARCH": "1", "CP_EVAL_WINDOWS": "1",
+                                                             "CP_ATTN_MODE": "ring", "CP_ROTATOR": "p2p"}, nproc=2, stdin=stdin)
+    lines = [l for l in out.splitlines() if l.startswith(("PPL", "ERR"))]
+    assert [l.split()[0] for l in lines] == ["PPL", "ERR", "PPL", "PPL"]
+    assert lines[0] == lines[3] and lines[0] != lines[2]                  # the cache swap takes effect and is reversible
+
+
+def test_cream_longrope_dumps_and_mem_probe(tmp_path):
+    fac = tmp_path / "f.txt"
+    fac.write_text("n_hat=0\ns=4\nsearch_len=256\n1.0 2.0 3.0 4.0\n")
+    out = run("context_parallelism_b200.trainers.llama_cp", {"CP_CKPT": "0", "CP_MAX_STEPS": "2", "CP_CREAM_MODE": "cream", "YARN_SCALE": "4",
+                                                             "YARN_ORIG_MAXPOS": "16", "CP_CREAM_LOG": "1", "CP_LONGROPE_FACTORS": fac,
+                                                             "CP_LOG_DIR": tmp_path})
+    assert out.count("[CREAM] step") == 2 and "[LongRoPE]" in out
+    rope = tmp_path / "rope.bin"
+    run("context_parallelism_b200.trainers.llama_cp", {"CP_CKPT": "0", "CP_DUMP_ROPE": rope, "CP_DUMP_ROPE_SEQLEN": "8", "YARN_SCALE": "2",
+                                                       "YARN_ORIG_MAXPOS": "32"})
+    from context_parallelism_b200.utils import ckpt
+    assert ckpt.read_named(str(rope))["rope_cache"].shape == (8, 8)
+    named = tmp_path / "named.bin"
+    run("context_parallelism_b200.trainers.llama_cp", {"CP_CKPT": "0", "CP_DUMP_NAMED": named})
+    assert list(ckpt.read_named(str(named)))[:4] == ["layers.0.q_gamma", "layers.0.k_gamma", "layers.0.attn_norm", "layers.0.wQ"]
+    out = run("context_parallelism_b200.trainers.llama_cp", {"CP_MEM_PROBE": "1", "CP_MEM_PROBE_STEPS": "2", "MEM_SNAPSHOT_DIR": tmp_path / "snap",
+                                                             "CP_MODEL_LABEL": "tiny", "CP_LOG_DIR": tmp_path})
+    snaps = list((tmp_path / "snap").glob("*.txt"))
+    assert len(snaps) == 1 and snaps[0].read_text().startswith("# impl=B200 label=tiny")
+
+
+def test_gpt2_trainer_named_init_and_generation(tmp_path):
+    env = {"CP_N_KVHEAD": "4", "CP_FFN": "128", "CP_CKPT": "0", "CP_MAX_STEPS": "5", "CP_LOG_DIR": tmp_path, "CP_GENERATE": "1",
+           "CP_VAL_FREQ": "2", "SAVE_INIT_NAMED": tmp_path / "init_weights_named_44M.bin", "DUMP_STEP0_GRADS": "1", "CP_ATTN_MODE": "ring",
+           "CP_ROTATOR": "p2p", "CP_WEIGHT_TYING": "1"}
+    out = run("context_parallelism_b200.trainers.gpt2_cp", env, nproc=2)
+    assert "sample tokens:" in out and "step     4" in out
+    grads = [l.split(",") for l in open(tmp_path / "step0_grads_b200.csv")]
+    assert grads[0][0] == "transformer.wte.weight" and float(grads[0][1]) > 0
+    # a second run that loads the saved init reproduces the first loss exactly
+    first = [l for l in out.splitlines() if l.startswith("step     0")][0]
+    out2 = run("context_parallelism_b200.trainers.gpt2_cp", dict(env, LOAD_INIT_NAMED=env["SAVE_INIT_NAMED"], CP_SEED="999", SAVE_INIT_NAMED=""), nproc=2)
+    first2 = [l for l in out2.splitlines() if l.startswith("step     0")][0]
+    assert first.split("|")[1] == first2.split("|")[1]
