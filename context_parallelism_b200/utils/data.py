@@ -96,5 +96,5 @@ class SyntheticLoader:
 
 def make_loader(cfg, split: str, dp_rank: int, dp_size: int):
     if cfg.synthetic or not cfg.data_root:
-        return SyntheticLoader(cfg.vocab_size, cfg.B, cfg.T, dp_rank, dp_size, cfg.seed + (0 if split == "train" else 7919))
+        return SyntheticLoader(cfg.vocab_size, cfg.B, cfg.T, dp_rank, dp_size, 0 if split == "train" else 7919)   # data seed 0, independent of the weight-init seed
     return ShardLoader(cfg.data_root, split, cfg.B, cfg.T, dp_rank, dp_size)
