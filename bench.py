@@ -38,6 +38,9 @@ MODELS = {
     # BASELINE config 2: GPT-2 124M
     "gpt2_124m": dict(family="gpt2", n_embd=768, n_layer=12, n_head=12, n_kv_head=12, head_dim=64, ffn_hidden=3072,
                       vocab_size=50257, weight_tying=True),
+    # profiling-sized: the 1B layer shapes with 2 layers and a small vocabulary (a few GB on the device)
+    "small": dict(family="llama", n_embd=2048, n_layer=2, n_head=32, n_kv_head=8, head_dim=64, ffn_hidden=8192,
+                  vocab_size=8192, weight_tying=False, rope_theta=5e5),
     "tiny": dict(family="llama", n_embd=512, n_layer=2, n_head=8, n_kv_head=2, head_dim=64, ffn_hidden=1024,
                  vocab_size=8192, weight_tying=False, rope_theta=5e5),
 }
