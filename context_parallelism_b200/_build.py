@@ -70,7 +70,8 @@ def _compile_one(src: Path, verbose: bool, ptxas_v: bool) -> Path:
     if nccl_inc:
         incs += ["-I", nccl_inc]
     if src.suffix == ".cu":
-        cmd = [f"{cuda}/bin/nvcc", *NVCC_FLAGS, *(["-Xptxas", "-v"] if ptxas_v else []), *incs, "-c", str(src), "-o", str(obj)]
+        cmd = [f"{cuda}/bin/nvcc", *NVCC_FLAGS, *os.environ.get("CPB_NVCC_EXTRA", "").split(),
+               *(["-Xptxas", "-v"] if ptxas_v else []), *incs, "-c", str(src), "-o", str(obj)]
     else:
         cmd = ["g++", *CXX_FLAGS, *incs, "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -1,6 +1,7 @@
 """Host wrapper of the tcgen05 flash-attention backward (``csrc/kernels/attention_bwd.cu``)."""
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -9,6 +10,8 @@ from .. import _native as nv
 from .attention import _ok_layout, _strides
 
 _INT_MAX = 2 ** 31 - 1
+# CPB_BWD_GENERAL=1 routes head_dim 64 through the general kernel as well (comparison / fallback)
+_USE_GENERAL_D64 = os.environ.get("CPB_BWD_GENERAL", "0") == "1"
 
 
 def padded_q_pos(Tq: int, device, q_pos: Optional[torch.Tensor]) -> torch.Tensor:
@@ -63,6 +66,20 @@ def flash_bwd_core(q, k, v, do, lse2, delta, qpos_pad, scale, causal, k_off, dq_
     st = nv.status_for(q.device)
     qs, ks = _strides(q), _strides(k)
     assert v.stride() == k.stride()
+    if D == 64 and not _USE_GENERAL_D64:
+        # head_dim 64 kernel (csrc/kernels/attention_bwd64.cu): the per-row vectors enter the tensor-core products as
+        # three-term bf16 splits, produced here from the fp32 vectors (a few tens of microseconds)
+        n = lse2.numel()
+        aug = torch.empty((2, n, 8), dtype=torch.bfloat16, device=q.device)
+        nv.call("flash_bwd64_aug", nv.ptr(lse2), nv.ptr(delta), nv.ptr(aug[0]), nv.ptr(aug[1]), nv.l(n), nv.f(scale),
+                nv.stream_ptr(q.device))
+        nv.call("flash_bwd64", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(do), nv.ptr(aug[0]), nv.ptr(aug[1]), nv.ptr(dq_f32),
+                nv.ptr(dk), nv.ptr(dv), nv.i(B), nv.i(Tq), nv.i(Tk), nv.i(Hq), nv.i(Hkv), nv.i(lse2.shape[-1]),
+                nv.l(qs[0]), nv.l(qs[1]), nv.l(qs[2]), nv.l(ks[0]), nv.l(ks[1]), nv.l(ks[2]),
+                nv.f(scale), nv.i(causal), nv.i(k_off), nv.ptr(qpos_pad), nv.i(2 if route is not None else int(dkv_accumulate)),
+                nv.ptr(route[0] if route else None), nv.ptr(route[1] if route else None),
+                nv.i(route[2] if route else 0), nv.i(route[3] if route else 0), st.ptr(), nv.stream_ptr(q.device))
+        return
     nv.call("flash_bwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(do), nv.ptr(lse2), nv.ptr(delta), nv.ptr(dq_f32),
             nv.ptr(dk), nv.ptr(dv), nv.i(B), nv.i(Tq), nv.i(Tk), nv.i(Hq), nv.i(Hkv), nv.i(D), nv.i(lse2.shape[-1]),
             nv.l(qs[0]), nv.l(qs[1]), nv.l(qs[2]), nv.l(ks[0]), nv.l(ks[1]), nv.l(ks[2]),

@@ -91,15 +91,21 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
 #ifndef CPB_WAIT_SPINS
 #define CPB_WAIT_SPINS (100000u)
 #endif
+#ifndef CPB_WAIT_FAST_SPINS
+#define CPB_WAIT_FAST_SPINS 256
+#endif
 #ifndef CPB_WAIT_HINT_NS
 #define CPB_WAIT_HINT_NS (20000u)
 #endif
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int site) {
+// Out of line on purpose: the warp-specialised kernels wait in dozens of places, and their hot loops must stay small
+// enough for the instruction cache.  Reached only when the first probe of the barrier fails.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                   int* status, int site) {
   // short waits (the common case inside a pipelined kernel) spin; long waits are parked by the hardware
 #pragma unroll 1
-  for (int it = 0; it < 256; ++it)
+  for (int it = 0; it < CPB_WAIT_FAST_SPINS; ++it)
     if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
   for (uint32_t it = 0; it < CPB_WAIT_SPINS; ++it) {
     if (mbar_try_wait_hint(bar, parity, CPB_WAIT_HINT_NS)) return true;
     if (*abort_flag) return false;
@@ -107,6 +113,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   *abort_flag = 1;
   report(status, ST_TIMEOUT_MBAR, site, (int)parity);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int site) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, site);
 }
 
 // ------------------------------------------------------------------ proxies / fences
@@ -246,6 +257,68 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// Lean issue path.  One thread issues every MMA of a CTA, and at N <= 128 an MMA lasts only 45-64 cycles, so the
+// scalar instructions between two MMAs decide the tensor-core rate.  A descriptor is kept as two 32-bit halves: the
+// start-address field is lo[13:0] in 16-byte units, so stepping it by a byte offset (address stays below 256 KB) is
+// one 32-bit add with an immediate; the accumulate flag is a template constant unless it depends on the iteration.
+struct SDesc { uint32_t lo, hi; };
+__device__ __forceinline__ SDesc sdesc_split(uint64_t d) { return SDesc{(uint32_t)d, (uint32_t)(d >> 32)}; }
+__device__ __forceinline__ uint64_t sdesc_at(SDesc d, uint32_t byte_off) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(d.lo + (byte_off >> 4)), "r"(d.hi));
+  return r;
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_ss_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
+}
+// The same, issued by the elected lane of a warp that runs the surrounding code convergently: operands that are
+// warp-uniform can then stay in uniform registers instead of being moved there before every MMA.
+template <bool ACC>
+__device__ __forceinline__ void umma_ss_cp(uint32_t leader, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0), "r"(leader) : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_ts_cp(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0), "r"(leader) : "memory");
+}
+__device__ __forceinline__ void umma_ts_p(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader) : "memory");
+}
+__device__ __forceinline__ void umma_commit_p(uint32_t leader, uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(leader) : "memory");
+}
 // Arrive on `bar` once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
@@ -253,14 +326,19 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 }
 
 // ------------------------------------------------------------------ small math helpers
+#ifdef CPB_PROF_ORDER      // diagnostic builds: keep the math between the clock reads that bracket it
+#define CPB_MATH_ASM asm volatile
+#else
+#define CPB_MATH_ASM asm
+#endif
 __device__ __forceinline__ float ex2f(float x) {
   float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  CPB_MATH_ASM("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  CPB_MATH_ASM("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
