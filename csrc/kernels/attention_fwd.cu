@@ -186,43 +186,50 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_kv > 0) {
+    // The whole warp runs this code convergently and only the elected lane issues: the descriptors then stay
+    // warp-uniform, and stepping one is a single add (see sdesc_at).
+    if (n_kv > 0) {
+      const uint32_t leader = elect_one() ? 1u : 0u;
       constexpr uint32_t idesc_qk = make_idesc_bf16(FA_BQ, FA_BK, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(FA_BQ, D, false, true);
-      const uint32_t sq = smem_u32(smem);
+      const SDesc dq = sdesc_split(sdesc_kmajor(smem_u32(smem)));
+      const SDesc dk0 = sdesc_split(sdesc_kmajor(smem_u32(smem + L::K_OFF)));                            // stage 0
+      const SDesc dv0 = sdesc_split(make_sdesc(smem_u32(smem + L::V_OFF), FA_BK * 128, 1024));           // V tile, N-major
       const uint32_t s_tmem = tmem_base;
       const uint32_t o_tmem = tmem_base + O_COL;
       auto issue_qk = [&](int j) {
-        const uint32_t sk = smem_u32(smem + L::K_OFF + (j & 1) * L::KV_BYTES);
+        const SDesc dk = SDesc{dk0.lo + (uint32_t)(j & 1) * (L::KV_BYTES >> 4), dk0.hi};
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k / 4) * (FA_BQ * 128) + (k % 4) * 32;
-          umma_ss(s_tmem, sdesc_kmajor(sq + off), sdesc_kmajor(sk + off), idesc_qk, k != 0);
+          if (k == 0) umma_ss_cp<false>(leader, s_tmem, sdesc_at(dq, off), sdesc_at(dk, off), idesc_qk);
+          else umma_ss_cp<true>(leader, s_tmem, sdesc_at(dq, off), sdesc_at(dk, off), idesc_qk);
         }
-        umma_commit(s_full);
+        umma_commit_p(leader, s_full);
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 600) && mbar_wait(&k_full[0], 0, abort_flag, p.status, 601);
+      ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
         issue_qk(0);
         for (int j = 0; j < n_kv; ++j) {
           const int st = j & 1;
-          if (!mbar_wait(p_full, j & 1, abort_flag, p.status, 602)) break;
-          if (!mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, p.status, 603)) break;
+          bool w = mbar_wait(p_full, j & 1, abort_flag, p.status, 602) && mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, p.status, 603);
+          if (!__all_sync(0xffffffffu, w)) break;
           tc_fence_after();
-          const uint32_t sv = smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
+          const SDesc dv = SDesc{dv0.lo + (uint32_t)st * (L::KV_BYTES >> 4), dv0.hi};
+          // A = P (bf16, 8 tensor-memory columns per 16 keys); B = V tile, N-major: 16 key rows = 2 KB
+          umma_ts_p(leader, o_tmem, s_tmem, sdesc_at(dv, 0), idesc_pv, j != 0);
 #pragma unroll
-          for (int k = 0; k < FA_BK / 16; ++k) {
-            // A = P (bf16, 8 tensor-memory columns per 16 keys); B = V tile, N-major: 16 key rows = 2 KB
-            umma_ts(o_tmem, s_tmem + (k >> 2) * 64 + (k & 3) * 8, make_sdesc(sv + k * 2048, FA_BK * 128, 1024), idesc_pv, (j | k) != 0);
-          }
-          umma_commit(&kv_empty[st]);
+          for (int k = 1; k < FA_BK / 16; ++k)
+            umma_ts_cp<true>(leader, o_tmem, s_tmem + (k >> 2) * 64 + (k & 3) * 8, sdesc_at(dv, k * 2048), idesc_pv);
+          umma_commit_p(leader, &kv_empty[st]);
           if (j + 1 < n_kv) {
-            if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 604)) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 604))) break;
             tc_fence_after();
             issue_qk(j + 1);
           } else {
-            umma_commit(o_done);
+            umma_commit_p(leader, o_done);
           }
         }
       }

@@ -132,32 +132,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop convergently and only the elected lane issues, so that the descriptors stay
+    // warp-uniform and stepping one is a single add: at BN = 128 an MMA lasts 64 cycles, and the scalar work between
+    // two of them must stay well below that.
+    {
+      const uint32_t leader = elect_one() ? 1u : 0u;
       constexpr uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, A_MN, B_MN);
+      const uint32_t s0 = smem_u32(smem);
+      const SDesc da0 = sdesc_split(A_MN ? make_sdesc(s0, 8192, 1024) : sdesc_kmajor(s0));                       // stage 0
+      const SDesc db0 = sdesc_split(B_MN ? make_sdesc(s0 + L::A_BYTES, 8192, 1024) : sdesc_kmajor(s0 + L::A_BYTES));
+      constexpr uint32_t A_STEP = A_MN ? 2048 : 32, B_STEP = B_MN ? 2048 : 32;
       int stage = 0; uint32_t phase = 0;
       int it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 200)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 200))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201)) break;
+          if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201))) { alive = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
-          const uint32_t sb = sa + L::A_BYTES;
+          const uint32_t so = (uint32_t)stage * (L::STAGE_BYTES >> 4);
+          const SDesc da = SDesc{da0.lo + so, da0.hi}, db = SDesc{db0.lo + so, db0.hi};
+          umma_ss_p(leader, d_tmem, sdesc_at(da, 0), sdesc_at(db, 0), idesc, kb != 0);
 #pragma unroll
-          for (int k = 0; k < GEMM_BK / 16; ++k) {
-            const uint64_t da = A_MN ? make_sdesc(sa + k * 2048, 8192, 1024) : sdesc_kmajor(sa + k * 32);
-            const uint64_t db = B_MN ? make_sdesc(sb + k * 2048, 8192, 1024) : sdesc_kmajor(sb + k * 32);
-            umma_ss(d_tmem, da, db, idesc, (kb | k) != 0);
-          }
-          umma_commit(&empty_bar[stage]);
+          for (int k = 1; k < GEMM_BK / 16; ++k)
+            umma_ss_cp<true>(leader, d_tmem, sdesc_at(da, k * A_STEP), sdesc_at(db, k * B_STEP), idesc);
+          umma_commit_p(leader, &empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        umma_commit(&tfull_bar[acc]);
-        if (*abort_flag) break;
+        umma_commit_p(leader, &tfull_bar[acc]);
       }
     }
   } else {
