@@ -122,7 +122,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
-    mbar_init(s_full, 1); mbar_init(p_full, 256); mbar_init(dq_full, 1); mbar_init(dq_empty, 128); mbar_init(acc_done, 1);
+    mbar_init(s_full, 1); mbar_init(p_full, 8); mbar_init(dq_full, 1); mbar_init(dq_empty, 4); mbar_init(acc_done, 1);
     mbar_init(&ds_empty[0], 1); mbar_init(&ds_empty[1], 1);
     *abort_flag = 0;
     *qt_start_s = num_q_tiles;
@@ -350,7 +350,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive_warp(p_full);
     }
     // final: dK, dV -> global
     if (n_it == 0) {
@@ -443,7 +443,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             *(float4*)(rowp + ((c4 ^ (r & 7)) << 4)) = make_float4(__uint_as_float(v[4 * c4]) * p.scale, __uint_as_float(v[4 * c4 + 1]) * p.scale,
                                                                    __uint_as_float(v[4 * c4 + 2]) * p.scale, __uint_as_float(v[4 * c4 + 3]) * p.scale);
         }
-        if (rnd == D / (32 * NB) - 1) { tc_fence_before(); mbar_arrive(dq_empty); }   // tensor-memory dQ is free again
+        if (rnd == D / (32 * NB) - 1) { tc_fence_before(); mbar_arrive_warp(dq_empty); }   // tensor-memory dQ is free again
         fence_proxy_async_smem();
         asm volatile("bar.sync 5, 128;" ::: "memory");
         if (issuer && !p.debug_skip_dq) {

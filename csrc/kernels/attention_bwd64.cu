@@ -73,8 +73,8 @@ struct Bwd64Smem {
   static constexpr int Q_OFF = 2 * TILE;
   static constexpr int DO_OFF = Q_OFF + NST * TILE;
   static constexpr int DS_OFF = DO_OFF + NST * TILE;      // dS^T 128 keys x 128 queries bf16 (32 KB)
-  static constexpr int DQS_OFF = DS_OFF + 32768;          // dQ staging: one box 128 x 32 fp32 (16 KB)
-  static constexpr int ONES_OFF = DQS_OFF + 16384;        // [128 x 8] bf16 (1,1,1,0,...)           2 KB
+  static constexpr int DQS_OFF = DS_OFF + 32768;          // dQ staging: per drain warp two boxes of 32 rows x 32 fp32 (4 x 8 KB)
+  static constexpr int ONES_OFF = DQS_OFF + 32768;        // [128 x 8] bf16 (1,1,1,0,...)           2 KB
   static constexpr int AUGL_OFF = ONES_OFF + 2048;        // NST x 2 KB
   static constexpr int AUGD_OFF = AUGL_OFF + NST * 2048;  // NST x 2 KB
   static constexpr int ZERO_OFF = AUGD_OFF + NST * 2048;        // zero block: second K chunk of every augmenting tile (after them: offsets > 0)
@@ -97,6 +97,12 @@ __device__ __forceinline__ uint64_t make_sdesc_noswz(uint32_t smem_addr, uint32_
 __device__ __forceinline__ void bulk_load_1d_64(void* smem, const void* gmem, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(smem)), "l"((uint64_t)gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// A global load that stays where it is written (the compiler would otherwise sink it to its first use, one tile later).
+__device__ __forceinline__ int ld_pinned_s32(const int* ptr) {
+  int v;
+  asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(ptr));
+  return v;
 }
 __device__ __forceinline__ void red_add_v4_64(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
@@ -137,8 +143,8 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < NST; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
-    mbar_init(s_ready, 1); mbar_init(s_consumed, 256); mbar_init(dp_ready, 1);
-    mbar_init(p_full, 256); mbar_init(dq_full, 1); mbar_init(dq_empty, 128); mbar_init(acc_done, 1); mbar_init(prof_bar, 1);
+    mbar_init(s_ready, 1); mbar_init(s_consumed, 8); mbar_init(dp_ready, 1);
+    mbar_init(p_full, 8); mbar_init(dq_full, 1); mbar_init(dq_empty, 4); mbar_init(acc_done, 1); mbar_init(prof_bar, 1);
     *abort_flag = 0;
     *qt_start_s = num_q_tiles;
     fence_mbar_init();
@@ -236,14 +242,8 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         umma_ss_cp<true>(leader, t_dp, d_ones, make_sdesc_noswz(sA, sZero - sA, 128), idesc_s);
         umma_commit_p(leader, dp_ready);
       };
-      const bool do_prof = B64_PROF_ON(p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
-      const bool wr_prof = do_prof && lane == 0;
-      long long pr[4] = {0, 0, 0, 0}, t0 = 0, t1 = 0;
-      uint32_t prof_ph = 0;
-      const bool gprof = do_prof && p.group_prof;
-#define B64_GROUP(i, e) do { if (gprof && (i) >= 64 && (i) < 72) { umma_commit_p(leader, prof_bar); mbar_wait(prof_bar, prof_ph & 1, abort_flag, p.status, 990); ++prof_ph; __syncwarp(); } B64_STAMP(wr_prof, i, e); } while (0)
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, 900) && mbar_wait(&q_full[0], 0, abort_flag, p.status, 901);
-      ok = __all_sync(0xffffffffu, ok);
+      const bool wr_prof = B64_PROF_ON(p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0);
+      bool ok = __all_sync(0xffffffffu, mbar_wait(kv_full, 0, abort_flag, p.status, 900) && mbar_wait(&q_full[0], 0, abort_flag, p.status, 901));
       if (ok) {
         tc_fence_after();
         issue_s(0);
@@ -252,7 +252,6 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int i = 0; ok && i < n_it; ++i) {
         const int st = i % NST;
         const SDesc qn = SDesc{dQ_n.lo + st * (L::TILE >> 4), dQ_n.hi}, gn = SDesc{dDO_n.lo + st * (L::TILE >> 4), dDO_n.hi};
-        if (do_prof) t0 = clock64();
         if (i + 1 < n_it) {
           // the warps have read S'(i): the next score tile can be produced while they work on tile i
           if (!__all_sync(0xffffffffu, mbar_wait(s_consumed, i & 1, abort_flag, p.status, 902))) break;
@@ -261,43 +260,40 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tc_fence_after();
           B64_STAMP(wr_prof, i, 1);
           issue_s((i + 1) % NST);
-          B64_GROUP(i, 2);
+          B64_STAMP(wr_prof, i, 2);
         }
-        if (do_prof) { t1 = clock64(); pr[0] += t1 - t0; }
         if (!__all_sync(0xffffffffu, mbar_wait(p_full, i & 1, abort_flag, p.status, 904))) break;
         tc_fence_after();
-        if (do_prof) { t0 = clock64(); pr[1] += t0 - t1; }
         B64_STAMP(wr_prof, i, 3);
         umma_ts_p(leader, t_dk, t_dp, sdesc_at(qn, 0), idesc_acc, i != 0);            // dK += dS^T Q  (frees the dS^T alias)
 #pragma unroll
         for (int k = 1; k < B64_T / 16; ++k)
           umma_ts_cp<true>(leader, t_dk, t_dp + (k >> 2) * 64 + (k & 3) * 8, sdesc_at(qn, k * 2048), idesc_acc);
-        B64_GROUP(i, 4);
+        B64_STAMP(wr_prof, i, 4);
         if (i + 1 < n_it) issue_dp((i + 1) % NST);                                     // dP'(i+1): early, off the warps' critical path
-        B64_GROUP(i, 5);
+        B64_STAMP(wr_prof, i, 5);
         umma_ts_p(leader, t_dv, t_pt, sdesc_at(gn, 0), idesc_acc, i != 0);            // dV += P^T dO
 #pragma unroll
         for (int k = 1; k < B64_T / 16; ++k)
           umma_ts_cp<true>(leader, t_dv, t_pt + k * 8, sdesc_at(gn, k * 2048), idesc_acc);
-        if (do_prof) t1 = clock64();
-        B64_GROUP(i, 6);
+        umma_commit_p(leader, &q_empty[st]);    // Q(i), dO(i) and their vectors are free
+        B64_STAMP(wr_prof, i, 6);
         if (i > 0 && !__all_sync(0xffffffffu, mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 905))) break;
         tc_fence_after();
-        if (do_prof) { pr[2] += clock64() - t1; }
         B64_STAMP(wr_prof, i, 7);
         umma_ss_cp<false>(leader, t_dq, sdesc_at(dDS_m, 0), sdesc_at(dK_n, 0), idesc_dq);      // dQ = dS K
 #pragma unroll
         for (int k = 1; k < B64_T / 16; ++k)
           umma_ss_cp<true>(leader, t_dq, sdesc_at(dDS_m, k * 2048), sdesc_at(dK_n, k * 2048), idesc_dq);
-        umma_commit_p(leader, dq_full);       // also: dV(i) has read P^T, dQ(i) the shared-memory dS^T
-        umma_commit_p(leader, &q_empty[st]);
-        B64_GROUP(i, 8);
-        if (do_prof) pr[3] += clock64() - t0;
+        umma_commit_p(leader, dq_full);         // also: dV(i) has read P^T, dQ(i) the shared-memory dS^T
+        B64_STAMP(wr_prof, i, 8);
       }
       umma_commit_p(leader, acc_done);
-      if (wr_prof) { for (int z = 0; z < 4; ++z) p.prof[z] = pr[z]; p.prof[15] = n_it; }
+#ifdef CPB_BWD64_PROF
+      if (wr_prof) p.prof[15] = n_it;
+#endif
     }
-  } else if (warp < 10) {
+  } else if (warp >= 2 && warp < 10) {
     // ------------------------------------------------------------------ softmax-gradient warps (thread = key row, 64 queries)
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;                   // which 64 query columns of the tile this thread owns
@@ -311,14 +307,16 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     bool alive = true;
     const bool wprof = B64_PROF_ON(p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64);
     // first query position of a tile decides whether it needs masking; read one tile ahead, straight from global memory
-    int qmin_next = n_it > 0 ? __ldg(p.q_pos + qt_start * B64_T) : 0;
+    int qmin_next = n_it > 0 ? ld_pinned_s32(p.q_pos + qt_start * B64_T) : 0;
     for (int i = 0; i < n_it && alive; ++i) {
       const int st = i % NST;
       const int qmin = qmin_next;
-      if (i + 1 < n_it) qmin_next = __ldg(p.q_pos + (qt_start + (i + 1) % n_qt) * B64_T);
+      if (i + 1 < n_it) qmin_next = ld_pinned_s32(p.q_pos + (qt_start + (i + 1) % n_qt) * B64_T);
       // slow path only for tiles that touch the causal diagonal or the end of the key sequence
       const bool need_mask = (k0 + B64_T > p.Tk) || (p.causal && (p.k_off + k0 + B64_T - 1 > qmin));
+      B64_STAMP(wprof, i, 16);
       bool ok = mbar_wait(s_ready, i & 1, abort_flag, p.status, 1001);
+      B64_STAMP(wprof, i, 17);
       if (need_mask) ok = ok && mbar_wait(&q_full[st], (i / NST) & 1, abort_flag, p.status, 1000);   // query positions in shared memory
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { alive = false; break; }
@@ -330,7 +328,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int ch = 0; ch < 4; ++ch) tmem_ld16(t_lane + ST_COL + cbase + 16 * ch, sv[ch]);
       tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(s_consumed);                          // the next score tile may overwrite S'^T
+      mbar_arrive_warp(s_consumed);                         // the next score tile may overwrite S'^T
       uint32_t pk[32];                                  // P^T of this thread's 64 queries, bf16 pairs
       if (!need_mask) {
 #pragma unroll
@@ -391,7 +389,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tmem_wait_st();
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive_warp(p_full);
       B64_STAMP(wprof, i, 15);
     }
     // final: dK, dV -> global
@@ -453,16 +451,17 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ dQ drain warps (10..13)
-    // tensor memory -> registers -> 128B-swizzled fp32 staging tile -> TMA reduce-add into the global fp32 dQ
-    // (rows past the end of the sequence are clipped by the tensor map).
+    // tensor memory -> registers -> 128B-swizzled fp32 staging -> TMA reduce-add into the global fp32 dQ (rows past the
+    // end of the sequence are clipped by the tensor map).  Every warp drains its own 32 query rows through its own
+    // staging slice with its own bulk group, so the four warps never wait for one another; the reduce of tile i is read
+    // out of the slice while the warp waits for tile i+1.
     const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;                  // query row inside the tile
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    uint8_t* stage = smem + L::DQS_OFF;
-    const bool issuer = (warp == 10 && lane == 0);
+    uint8_t* stage = smem + L::DQS_OFF + quarter * 8192;      // [2 column halves][32 rows][128 B]
+    const bool issuer = (lane == 0);
     if (issuer) tma_prefetch_desc(&tmDQ);
     for (int i = 0; i < n_it; ++i) {
-      const bool dprof = B64_PROF_ON(p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && issuer);
+      const bool dprof = B64_PROF_ON(p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 10 && issuer);
       const bool dprof_all = B64_PROF_ON(p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && i >= 64 && i < 72);
       bool ok = mbar_wait(dq_full, i & 1, abort_flag, p.status, 1100);
       ok = __all_sync(0xffffffffu, ok);
@@ -476,25 +475,27 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tmem_ld32(t_lane + DQ_COL + 32, v[1]);
       tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(dq_empty);                            // tensor-memory dQ is free again
+      mbar_arrive_warp(dq_empty);                          // tensor-memory dQ is free again
       if (dprof_all) atomicMax((unsigned long long*)&p.prof[16 + (i - 64) * 32 + 11], (unsigned long long)clock64());
+      if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous tile has left the slice
+      __syncwarp();
 #pragma unroll
-      for (int rnd = 0; rnd < D / 32; ++rnd) {          // one box of 128 x 32 fp32 per round through the staging tile
-        uint8_t* rowp = stage + r * 128;
+      for (int h = 0; h < D / 32; ++h) {
+        uint8_t* rowp = stage + h * 4096 + lane * 128;
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4)                  // dS was formed without the softmax scale: apply it here
-          *(float4*)(rowp + ((c4 ^ (r & 7)) << 4)) = make_float4(__uint_as_float(v[rnd][4 * c4]) * p.scale, __uint_as_float(v[rnd][4 * c4 + 1]) * p.scale,
-                                                                 __uint_as_float(v[rnd][4 * c4 + 2]) * p.scale, __uint_as_float(v[rnd][4 * c4 + 3]) * p.scale);
-        fence_proxy_async_smem();
-        asm volatile("bar.sync 5, 128;" ::: "memory");
-        if (issuer && !p.debug_skip_dq) {
+          *(float4*)(rowp + ((c4 ^ (lane & 7)) << 4)) = make_float4(__uint_as_float(v[h][4 * c4]) * p.scale, __uint_as_float(v[h][4 * c4 + 1]) * p.scale,
+                                                                    __uint_as_float(v[h][4 * c4 + 2]) * p.scale, __uint_as_float(v[h][4 * c4 + 3]) * p.scale);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (issuer && !p.debug_skip_dq) {
+#pragma unroll
+        for (int h = 0; h < D / 32; ++h)
           asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                       ::"l"((uint64_t)&tmDQ), "r"(smem_u32(stage)), "r"(rnd * 32), "r"(hq), "r"(q0), "r"(b)
+                       ::"l"((uint64_t)&tmDQ), "r"(smem_u32(stage + h * 4096)), "r"(h * 32), "r"(hq), "r"(q0 + quarter * 32), "r"(b)
                        : "memory");
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        }
-        asm volatile("bar.sync 5, 128;" ::: "memory");                         // staging may be overwritten
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
       B64_STAMP(dprof, i, 13);
     }
@@ -577,7 +578,7 @@ extern "C" int cpb_flash_bwd64(const void* q, const void* k, const void* v, cons
   {
     uint64_t dims[4] = {(uint64_t)B64_D, (uint64_t)Hq, (uint64_t)Tq, (uint64_t)B};
     uint64_t strides[4] = {0, (uint64_t)B64_D * 4, (uint64_t)Hq * B64_D * 4, (uint64_t)Tq * Hq * B64_D * 4};
-    uint32_t box[4] = {32, 1, (uint32_t)B64_T, 1};
+    uint32_t box[4] = {32, 1, 32, 1};      // one drain warp: 32 query rows x 32 columns
     if ((rc = encode_tmap(&tdq, dq, 4, 4, dims, strides, box, 1)) != CPB_OK) return rc;
   }
   Bwd64Params p;
@@ -609,7 +610,7 @@ extern "C" int cpb_flash_bwd64(const void* q, const void* k, const void* v, cons
       const long long base = h[16 + 9];
       const int NE = 18;
       static const char* names[18] = {"M:s_consumed", "M:q_full", "M:S'issued", "M:p_full", "M:dK issued", "M:dP' issued", "M:dV issued", "M:dq_empty",
-                                      "M:dQ issued", "W:s_ready", "D:dq_full seen(last warp)", "D:dq_empty arrive(last warp)", "W:dp_ready", "D:staged", "W:dq_full", "W:p_full arrive", "M:dq_empty try_wait ok", "M:dq_empty all_sync"};
+                                      "M:dQ issued", "W:s_ready", "D:dq_full seen(last warp)", "D:dq_empty arrive(last warp)", "W:dp_ready", "D:staged", "W:dq_full", "W:p_full arrive", "W:tile top", "W:s_ready try ok"};
       for (int t = 0; t < 4; ++t) {
         fprintf(stderr, "  tile %d:", 64 + t);
         // chronological order
