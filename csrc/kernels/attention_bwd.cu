@@ -32,7 +32,6 @@
 
 namespace cpb {
 
-static __device__ long long g_bwd_prof[16];
 
 constexpr int FB_T = 128;            // tile edge (queries and keys)
 constexpr int FB_THREADS = 448;
@@ -55,7 +54,6 @@ struct BwdParams {
   const uint64_t* route_v;
   int route_rows, route_tl;
   int debug_skip_dq;        // diagnostic: do not add dQ tiles to global memory (timing experiments only)
-  long long* debug_prof;    // diagnostic: CTA (0,0,0) writes the MMA thread's cycle breakdown here (6 counters)
   int* status;
 };
 
@@ -180,107 +178,110 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_it > 0) {
+    // The whole warp runs this code convergently and only the elected lane issues, so that the descriptors stay
+    // warp-uniform and stepping one is a single add.
+    if (n_it > 0) {
+      const uint32_t leader = elect_one() ? 1u : 0u;
       constexpr uint32_t idesc_s = make_idesc_bf16(FB_T, FB_T, false, false);     // S, dP
       constexpr uint32_t idesc_acc = make_idesc_bf16(FB_T, D, true, true);         // dV, dK: A M-major smem, B N-major
       constexpr uint32_t idesc_dq = make_idesc_bf16(FB_T, D, false, true);         // dQ: A K-major smem, B N-major
-      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
-      const uint32_t sP = smem_u32(smem + L::PS_OFF), sDS = smem_u32(smem + L::DS_OFF);
-      if (mbar_wait(kv_full, 0, abort_flag, p.status, 900)) {
-        long long prof[6] = {0, 0, 0, 0, 0, 0};
-        const bool do_prof = p.debug_prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-        auto issue_scores = [&](uint32_t sQ, uint32_t sDO) {
+      const SDesc dK_k = sdesc_split(sdesc_kmajor(smem_u32(smem + L::K_OFF))), dV_k = sdesc_split(sdesc_kmajor(smem_u32(smem + L::V_OFF)));
+      const SDesc dK_n = sdesc_split(make_sdesc(smem_u32(smem + L::K_OFF), FB_T * 128, 1024));
+      const SDesc dQ_k0 = sdesc_split(sdesc_kmajor(smem_u32(smem + L::Q_OFF))), dDO_k0 = sdesc_split(sdesc_kmajor(smem_u32(smem + L::DO_OFF)));
+      const SDesc dQ_n0 = sdesc_split(make_sdesc(smem_u32(smem + L::Q_OFF), FB_T * 128, 1024));
+      const SDesc dDO_n0 = sdesc_split(make_sdesc(smem_u32(smem + L::DO_OFF), FB_T * 128, 1024));
+      const SDesc dP_m = sdesc_split(make_sdesc(smem_u32(smem + L::PS_OFF), FB_T * 128, 1024));
+      const SDesc dDS_m0 = sdesc_split(make_sdesc(smem_u32(smem + L::DS_OFF), FB_T * 128, 1024));
+      const SDesc dDS_k0 = sdesc_split(sdesc_kmajor(smem_u32(smem + L::DS_OFF)));
+      const uint32_t t_s = tmem_base + S_COL, t_dp = tmem_base + DP_COL, t_dv = tmem_base + DV_COL, t_dk = tmem_base + DK_COL, t_dq = tmem_base + DQ_COL;
+      auto stage = [](SDesc d, int st) { return SDesc{d.lo + (uint32_t)st * (L::TILE >> 4), d.hi}; };
+      auto issue_scores = [&](int st) {
+        const SDesc q = stage(dQ_k0, st), g = stage(dDO_k0, st);
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {       // S = Q K^T
-            const uint32_t off = (k / 4) * (FB_T * 128) + (k % 4) * 32;
-            umma_ss(tmem_base + S_COL, sdesc_kmajor(sQ + off), sdesc_kmajor(sK + off), idesc_s, k != 0);
-          }
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {       // dP = dO V^T
-            const uint32_t off = (k / 4) * (FB_T * 128) + (k % 4) * 32;
-            umma_ss(tmem_base + DP_COL, sdesc_kmajor(sDO + off), sdesc_kmajor(sV + off), idesc_s, k != 0);
-          }
-          umma_commit(s_full);
-        };
-        auto issue_dv = [&](uint32_t sDO, int i) {       // dV += P^T dO : contraction over the 128 queries (tile rows)
-#pragma unroll
-          for (int k = 0; k < FB_T / 16; ++k)
-            umma_ss(tmem_base + DV_COL, make_sdesc(sP + k * 2048, FB_T * 128, 1024), make_sdesc(sDO + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
-        };
-        auto issue_dk = [&](uint32_t sQ, uint32_t sDSi, int i) {   // dK += dS^T Q
-#pragma unroll
-          for (int k = 0; k < FB_T / 16; ++k)
-            umma_ss(tmem_base + DK_COL, make_sdesc(sDSi + k * 2048, FB_T * 128, 1024), make_sdesc(sQ + k * 2048, FB_T * 128, 1024), idesc_acc, (i | k) != 0);
-        };
-        auto issue_dq = [&](uint32_t sDSi) {             // dQ = dS K : contraction over the 128 keys (tile columns)
-#pragma unroll
-          for (int k = 0; k < FB_T / 16; ++k)
-            umma_ss(tmem_base + DQ_COL, sdesc_kmajor(sDSi + (k >> 2) * (FB_T * 128) + (k & 3) * 32), make_sdesc(sK + k * 2048, FB_T * 128, 1024), idesc_dq, k != 0);
-        };
-        if (OVERLAP) {
-          // Pipelined order (head_dim 64).  When the softmax-gradient warps finish tile i the issuer queues
-          //   dV(i) | S(i+1), dP(i+1) | dK(i), dQ(i)
-          // so the warps start on tile i+1 as soon as its score products are done while dK(i) and dQ(i), which
-          // read the double-buffered dS tile, still run on the tensor cores.  P is single-buffered: dV(i) is
-          // ordered before S(i+1), whose completion is what lets the warps overwrite P.
-          bool ok = mbar_wait(&q_full[0], 0, abort_flag, p.status, 901);
-          if (ok) {
-            tc_fence_after();
-            issue_scores(smem_u32(smem + L::Q_OFF), smem_u32(smem + L::DO_OFF));
-          }
-          for (int i = 0; ok && i < n_it; ++i) {
-            const int st = i % ST;
-            const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE), sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
-            const uint32_t sDSi = sDS + (i & 1) * (FB_T * FB_T * 2);
-            long long t0 = do_prof ? clock64() : 0;
-            if (!mbar_wait(p_full, i & 1, abort_flag, p.status, 903)) break;
-            if (do_prof) { long long t = clock64(); prof[2] += t - t0; t0 = t; }
-            tc_fence_after();
-            issue_dv(sDO, i);
-            if (i + 1 < n_it) {
-              const int sn = (i + 1) % ST;
-              if (!mbar_wait(&q_full[sn], ((i + 1) / ST) & 1, abort_flag, p.status, 901)) break;
-              tc_fence_after();
-              issue_scores(smem_u32(smem + L::Q_OFF + sn * L::TILE), smem_u32(smem + L::DO_OFF + sn * L::TILE));
-            }
-            if (do_prof) { long long t = clock64(); prof[1] += t - t0; t0 = t; }
-            issue_dk(sQ, sDSi, i);
-            if (i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 904)) break;
-            if (do_prof) { long long t = clock64(); prof[3] += t - t0; t0 = t; }
-            tc_fence_after();
-            issue_dq(sDSi);
-            umma_commit(&q_empty[st]);
-            umma_commit(&ds_empty[i & 1]);
-            umma_commit(dq_full);
-            if (do_prof) { long long t = clock64(); prof[4] += t - t0; prof[5] += 1; }
-          }
-        } else {
-          for (int i = 0; i < n_it; ++i) {
-            const int st = i % ST;
-            const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE), sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
-            long long t0 = do_prof ? clock64() : 0;
-            if (!mbar_wait(&q_full[st], (i / ST) & 1, abort_flag, p.status, 901)) break;
-            if (do_prof) { long long t = clock64(); prof[0] += t - t0; t0 = t; }
-            if (DQ_ALIAS && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 902)) break;
-            tc_fence_after();
-            issue_scores(sQ, sDO);
-            if (do_prof) { long long t = clock64(); prof[1] += t - t0; t0 = t; }
-            if (!mbar_wait(p_full, i & 1, abort_flag, p.status, 903)) break;
-            if (do_prof) { long long t = clock64(); prof[2] += t - t0; t0 = t; }
-            if (!DQ_ALIAS && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 904)) break;
-            if (do_prof) { long long t = clock64(); prof[3] += t - t0; t0 = t; }
-            tc_fence_after();
-            issue_dv(sDO, i);
-            issue_dk(sQ, sDS, i);
-            issue_dq(sDS);
-            umma_commit(&q_empty[st]);
-            umma_commit(dq_full);
-            if (do_prof) { long long t = clock64(); prof[4] += t - t0; prof[5] += 1; }
-          }
+        for (int k = 0; k < D / 16; ++k) {       // S = Q K^T
+          const uint32_t off = (k / 4) * (FB_T * 128) + (k % 4) * 32;
+          if (k == 0) umma_ss_cp<false>(leader, t_s, sdesc_at(q, off), sdesc_at(dK_k, off), idesc_s);
+          else umma_ss_cp<true>(leader, t_s, sdesc_at(q, off), sdesc_at(dK_k, off), idesc_s);
         }
-        if (do_prof) for (int z = 0; z < 6; ++z) p.debug_prof[z] = prof[z];
-        umma_commit(acc_done);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {       // dP = dO V^T
+          const uint32_t off = (k / 4) * (FB_T * 128) + (k % 4) * 32;
+          if (k == 0) umma_ss_cp<false>(leader, t_dp, sdesc_at(g, off), sdesc_at(dV_k, off), idesc_s);
+          else umma_ss_cp<true>(leader, t_dp, sdesc_at(g, off), sdesc_at(dV_k, off), idesc_s);
+        }
+        umma_commit_p(leader, s_full);
+      };
+      auto issue_dv = [&](int st, int i) {       // dV += P^T dO : contraction over the 128 queries (tile rows)
+        const SDesc g = stage(dDO_n0, st);
+        umma_ss_p(leader, t_dv, sdesc_at(dP_m, 0), sdesc_at(g, 0), idesc_acc, i != 0);
+#pragma unroll
+        for (int k = 1; k < FB_T / 16; ++k) umma_ss_cp<true>(leader, t_dv, sdesc_at(dP_m, k * 2048), sdesc_at(g, k * 2048), idesc_acc);
+      };
+      auto issue_dk = [&](int st, int buf, int i) {   // dK += dS^T Q
+        const SDesc q = stage(dQ_n0, st);
+        const SDesc ds = SDesc{dDS_m0.lo + (uint32_t)buf * ((FB_T * FB_T * 2) >> 4), dDS_m0.hi};
+        umma_ss_p(leader, t_dk, sdesc_at(ds, 0), sdesc_at(q, 0), idesc_acc, i != 0);
+#pragma unroll
+        for (int k = 1; k < FB_T / 16; ++k) umma_ss_cp<true>(leader, t_dk, sdesc_at(ds, k * 2048), sdesc_at(q, k * 2048), idesc_acc);
+      };
+      auto issue_dq = [&](int buf) {             // dQ = dS K : contraction over the 128 keys (tile columns)
+        const SDesc ds = SDesc{dDS_k0.lo + (uint32_t)buf * ((FB_T * FB_T * 2) >> 4), dDS_k0.hi};
+#pragma unroll
+        for (int k = 0; k < FB_T / 16; ++k) {
+          const uint32_t off = (k >> 2) * (FB_T * 128) + (k & 3) * 32;
+          if (k == 0) umma_ss_cp<false>(leader, t_dq, sdesc_at(ds, off), sdesc_at(dK_n, 0), idesc_dq);
+          else umma_ss_cp<true>(leader, t_dq, sdesc_at(ds, off), sdesc_at(dK_n, k * 2048), idesc_dq);
+        }
+      };
+      bool ok = __all_sync(0xffffffffu, mbar_wait(kv_full, 0, abort_flag, p.status, 900));
+      if (ok && OVERLAP) {
+        // Pipelined order (head_dim 64).  When the softmax-gradient warps finish tile i the issuer queues
+        //   dV(i) | S(i+1), dP(i+1) | dK(i), dQ(i)
+        // so the warps start on tile i+1 as soon as its score products are done while dK(i) and dQ(i), which
+        // read the double-buffered dS tile, still run on the tensor cores.  P is single-buffered: dV(i) is
+        // ordered before S(i+1), whose completion is what lets the warps overwrite P.
+        ok = __all_sync(0xffffffffu, mbar_wait(&q_full[0], 0, abort_flag, p.status, 901));
+        if (ok) {
+          tc_fence_after();
+          issue_scores(0);
+        }
+        for (int i = 0; ok && i < n_it; ++i) {
+          const int st = i % ST;
+          if (!__all_sync(0xffffffffu, mbar_wait(p_full, i & 1, abort_flag, p.status, 903))) break;
+          tc_fence_after();
+          issue_dv(st, i);
+          if (i + 1 < n_it) {
+            const int sn = (i + 1) % ST;
+            if (!__all_sync(0xffffffffu, mbar_wait(&q_full[sn], ((i + 1) / ST) & 1, abort_flag, p.status, 901))) break;
+            tc_fence_after();
+            issue_scores(sn);
+          }
+          issue_dk(st, i & 1, i);
+          if (i > 0 && !__all_sync(0xffffffffu, mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 904))) break;
+          tc_fence_after();
+          issue_dq(i & 1);
+          umma_commit_p(leader, &q_empty[st]);
+          umma_commit_p(leader, &ds_empty[i & 1]);
+          umma_commit_p(leader, dq_full);
+        }
+      } else if (ok) {
+        for (int i = 0; i < n_it; ++i) {
+          const int st = i % ST;
+          if (!__all_sync(0xffffffffu, mbar_wait(&q_full[st], (i / ST) & 1, abort_flag, p.status, 901))) break;
+          if (DQ_ALIAS && i > 0 && !__all_sync(0xffffffffu, mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 902))) break;
+          tc_fence_after();
+          issue_scores(st);
+          if (!__all_sync(0xffffffffu, mbar_wait(p_full, i & 1, abort_flag, p.status, 903))) break;
+          if (!DQ_ALIAS && i > 0 && !__all_sync(0xffffffffu, mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 904))) break;
+          tc_fence_after();
+          issue_dv(st, i);
+          issue_dk(st, 0, i);
+          issue_dq(0);
+          umma_commit_p(leader, &q_empty[st]);
+          umma_commit_p(leader, dq_full);
+        }
       }
+      umma_commit_p(leader, acc_done);
     }
   } else if (warp < 10) {
     // ------------------------------------------------------------------ softmax-gradient warps
@@ -562,12 +563,6 @@ extern "C" int cpb_flash_bwd(const void* q, const void* k, const void* v, const 
   {
     const char* e = getenv("CPB_BWD_SKIP_DQ");
     p.debug_skip_dq = (e != nullptr && e[0] == '1');
-    p.debug_prof = nullptr;
-    const char* pe = getenv("CPB_BWD_PROF");
-    if (pe != nullptr && pe[0] == '1') {
-      void* sym = nullptr;
-      if (cudaGetSymbolAddress(&sym, g_bwd_prof) == cudaSuccess) p.debug_prof = (long long*)sym;
-    }
   }
   if (dkv_f32_accumulate == 2 && (route_k == nullptr || route_v == nullptr || route_rows <= 0))
     return set_error(CPB_ERR_ARG, "flash_bwd: routed dK/dV needs route tables");
@@ -580,13 +575,6 @@ extern "C" int cpb_flash_bwd(const void* q, const void* k, const void* v, const 
     static bool cfg = false;
     if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::TOTAL)); cfg = true; }
     flash_bwd_kernel<128><<<grid, FB_THREADS, BwdSmem<128>::TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);
-  }
-  if (p.debug_prof != nullptr) {
-    long long h[6];
-    cudaStreamSynchronize(stream);
-    if (cudaMemcpy(h, p.debug_prof, sizeof(h), cudaMemcpyDeviceToHost) == cudaSuccess && h[5] > 0)
-      fprintf(stderr, "[flash_bwd prof] iters=%lld MMA-thread cycles per tile: wait_q=%lld issue_scores=%lld wait_p=%lld wait_dq=%lld issue_grads=%lld\n",
-              h[5], h[0] / h[5], h[1] / h[5], h[2] / h[5], h[3] / h[5], h[4] / h[5]);
   }
   return check_launch("flash_bwd");
 }
