@@ -67,7 +67,7 @@ class FusedComm:
         self.timeout_s = min(cfg.watchdog_s, 20.0)
         self._ring_state: Dict[tuple, "_RingBuffers"] = {}
         self._uly_state: Dict[tuple, "_UlyssesBuffers"] = {}
-        self._layer_counter = 0
+        self._layer_counter = {"ring": 0, "uly": 0}      # one slot sequence per exchange (hybrid runs both in every layer)
         self._ar_stage_off: Optional[int] = None
 
     # ------------------------------------------------------------------ construction
@@ -122,9 +122,9 @@ class FusedComm:
         nv.call("barrier", nv.ptr(g.peers), nv.l(g.flag_off), nv.i(g.size), nv.i(g.rank), nv.i(g.epoch),
                 ctypes.c_double(self.timeout_s), st.ptr(), nv.stream_ptr(self.device))
 
-    def next_layer_slot(self, n_layers: int) -> int:
-        s = self._layer_counter % n_layers
-        self._layer_counter += 1
+    def next_layer_slot(self, n_layers: int, kind: str = "ring") -> int:
+        s = self._layer_counter[kind] % n_layers
+        self._layer_counter[kind] += 1
         return s
 
     # ------------------------------------------------------------------ gradient all-reduce
@@ -347,7 +347,7 @@ class _FusedUlyssesFn(torch.autograd.Function):
         if ub is None:
             ub = fc._uly_state[key] = _UlyssesBuffers(fc, B, Tl, Hq, Hkv, D)
         g = fc.g_uly
-        slot = fc.next_layer_slot(fc.cfg.n_layer)
+        slot = fc.next_layer_slot(fc.cfg.n_layer, "uly")
         q, k, v = _seq_layout(q, Tl, D), _seq_layout(k, Tl, D), _seq_layout(v, Tl, D)
         # sequence -> head: peer stores straight into the head owners' landing buffers
         _a2a_push(fc, g, [(q, ub.nq, 1, 0), (k, ub.kvl, ub.rep, ub.nq), (v, ub.kvl, ub.rep, ub.nq + ub.kvl)],
@@ -391,3 +391,80 @@ class _FusedUlyssesFn(torch.autograd.Function):
         _a2a_pull(fc, g, [(dq, Hq, ub.nq, 1, 0, ub.nq, ub.dq_off), (dk, Hkv, ub.kvl, ub.rep, 0, ub.kvl, ub.dk_off),
                           (dv, Hkv, ub.kvl, ub.rep, 0, ub.kvl, ub.dv_off)], B, Tl, D)
         return dq, dk, dv, None, None
+
+
+# ============================================================================ hybrid: the Ulysses exchange on its own
+class _FusedSeqToHeadFn(torch.autograd.Function):
+    """``[B, Tl, H, D]`` (this rank's tokens, all heads) -> ``[B, Tl*P, H/P, D]`` (the whole ring block, this rank's
+    heads) for q, k and v at once, by peer stores into the head owners' per-layer landing buffers; the adjoint pulls
+    the gradients back (the exchange that ``hybrid_attention`` wraps around ring attention,
+    context_parallel/ContextParallel.h:1359-1396)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, fc: FusedComm):
+        B, Tl, Hq, D = q.shape
+        Hkv = k.shape[2]
+        key = (B, Tl, Hq, Hkv, D)
+        ub = fc._uly_state.get(key)
+        if ub is None:
+            ub = fc._uly_state[key] = _UlyssesBuffers(fc, B, Tl, Hq, Hkv, D)
+        g = fc.g_uly
+        slot = fc.next_layer_slot(fc.cfg.n_layer, "uly")
+        q, k, v = _seq_layout(q, Tl, D), _seq_layout(k, Tl, D), _seq_layout(v, Tl, D)
+        _a2a_push(fc, g, [(q, ub.nq, 1, 0), (k, ub.kvl, ub.rep, ub.nq), (v, ub.kvl, ub.rep, ub.nq + ub.kvl)],
+                  B, Tl, D, ub.hl, ub.qkv_off + slot * ub.qkv_bytes)
+        fc.barrier(g)
+        land = ub.qkv_view(fc, slot)
+        ctx.fc, ctx.ub = fc, ub
+        return land[:, :, :ub.nq], land[:, :, ub.nq:ub.nq + ub.kvl], land[:, :, ub.nq + ub.kvl:]
+
+    @staticmethod
+    def backward(ctx, dqh, dkh, dvh):
+        fc, ub = ctx.fc, ctx.ub
+        g = fc.g_uly
+        B, Tl, Hq, Hkv, D = ub.B, ub.Tl, ub.Hq, ub.Hkv, ub.D
+        ub.dq.copy_(dqh)
+        ub.dk.copy_(dkh)
+        ub.dv.copy_(dvh)
+        fc.barrier(g)
+        dqkv = torch.empty((B, Tl, Hq + 2 * Hkv, D), dtype=torch.bfloat16, device=fc.device)
+        dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
+        _a2a_pull(fc, g, [(dq, Hq, ub.nq, 1, 0, ub.nq, ub.dq_off), (dk, Hkv, ub.kvl, ub.rep, 0, ub.kvl, ub.dk_off),
+                          (dv, Hkv, ub.kvl, ub.rep, 0, ub.kvl, ub.dv_off)], B, Tl, D)
+        return dq, dk, dv, None
+
+
+class _FusedHeadToSeqFn(torch.autograd.Function):
+    """The reverse exchange for the attention output: ``[B, Tl*P, Hq/P, D]`` -> ``[B, Tl, Hq, D]``: the output is staged
+    in the arena, and every token owner pulls its rows of every head; the adjoint pushes dO to the head owners."""
+
+    @staticmethod
+    def forward(ctx, oh, fc: FusedComm, ub: "_UlyssesBuffers"):
+        g = fc.g_uly
+        B, Tl, Hq, D = ub.B, ub.Tl, ub.Hq, ub.D
+        ub.dq.copy_(oh)                     # the dQ staging buffer has the shape of the per-head-slice output; forward and backward never overlap
+        fc.barrier(g)
+        out = torch.empty((B, Tl, Hq, D), dtype=torch.bfloat16, device=fc.device)
+        _a2a_pull(fc, g, [(out, Hq, ub.nq, 1, 0, ub.nq, ub.dq_off)], B, Tl, D)
+        ctx.fc, ctx.ub = fc, ub
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        fc, ub = ctx.fc, ctx.ub
+        g = fc.g_uly
+        do = do.contiguous()
+        _a2a_push(fc, g, [(do, ub.nq, 1, 0)], ub.B, ub.Tl, ub.D, ub.nq, ub.do_off)
+        fc.barrier(g)
+        return ub.do, None, None
+
+
+def fused_seq_to_head(fc: FusedComm, q, k, v):
+    qh, kh, vh = _FusedSeqToHeadFn.apply(q, k, v, fc)
+    ub = fc._uly_state[(q.shape[0], q.shape[1], q.shape[2], k.shape[2], q.shape[3])]
+    return qh, kh, vh, ub
+
+
+def fused_head_to_seq(fc: FusedComm, oh, ub):
+    return _FusedHeadToSeqFn.apply(oh, fc, ub)
+

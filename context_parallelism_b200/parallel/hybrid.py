@@ -3,7 +3,8 @@
 The Ulysses combine over the inner group turns ``[B, T/(R·U), H, D]`` into ``[B, T/R, H/U, D]`` — the whole
 HeadTail ring block of this ring rank with a slice of the heads — then ring attention runs over the
 outer group and the result is partitioned back (context_parallel/ContextParallel.h:1359-1396,
-context_parallel/HybridUlyssesBackward.h:42-81).  Requires ``q_heads % U == 0`` and ``kv_heads % U == 0``.
+context_parallel/HybridUlyssesBackward.h:42-81).  Requires ``q_heads % U == 0`` and ``kv_heads % U == 0``.  With the fused transport both the ring (copy CTAs inside the
+attention kernel) and the Ulysses exchange (peer stores / pulls over the symmetric heap) run without NCCL.
 """
 from __future__ import annotations
 
@@ -16,7 +17,12 @@ def hybrid_attention(q, k, v, ctx, attn, fused: bool):
     U, R = ctx.ulysses_size, ctx.ring_size
     if q.shape[2] % U or k.shape[2] % U:
         raise ValueError("hybrid: q_heads and kv_heads must be multiples of the Ulysses degree")
-    if U > 1:
+    fused_uly = fused and U > 1 and getattr(ctx.fused, "g_uly", None) is not None and q.dtype == torch.bfloat16
+    ub = None
+    if fused_uly:
+        from .fused import fused_head_to_seq, fused_seq_to_head
+        q, k, v, ub = fused_seq_to_head(ctx.fused, q, k, v)
+    elif U > 1:
         q, k, v = (seq_to_head(t, ctx.ulysses_group) for t in (q, k, v))
     T = q.shape[1] * R
     if R > 1:
@@ -30,6 +36,8 @@ def hybrid_attention(q, k, v, ctx, attn, fused: bool):
     else:
         from ..ops import attention as A
         o, _ = A.flash_attention(q, k, v, attn.scale, True)
-    if U > 1:
+    if fused_uly:
+        o = fused_head_to_seq(ctx.fused, o, ub)
+    elif U > 1:
         o = head_to_seq(o, ctx.ulysses_group)
     return o

@@ -20,6 +20,7 @@
 // Replaces fused_attn_forward_kernel_tc (context_parallel/AttentionForward.cu:490-844) and
 // gqa_fused_rope_v2 (context_parallel/GQA_fused_fwd_sm103_cp.cu:117-281).
 #include "common.cuh"
+#include <stdio.h>
 #include "host_utils.h"
 #include "ring_copy.cuh"
 
@@ -28,7 +29,8 @@ namespace cpb {
 constexpr int FA_BQ = 128;
 constexpr int FA_BK = 128;
 constexpr int FA_THREADS = 320;
-constexpr int FA_STAGES = 2;
+constexpr int FA_KSTAGES = 3;      // K is wanted one tile ahead of V (the next score tile overlaps the softmax of this one)
+constexpr int FA_VSTAGES = 2;
 
 struct FwdParams {
   int B, Tq, Tk, Hq, Hkv;
@@ -58,13 +60,22 @@ struct FwdParams {
   int* status;
 };
 
+// Diagnostics: with -DCPB_FWD_PROF the CTA that owns the last query tile of (head 0, batch 0) records an event
+// timeline of K/V tiles 32..35 into a static device array that the launcher prints.
+#ifdef CPB_FWD_PROF
+static __device__ long long g_fwd_prof[4 * 16];
+#define FWD_STAMP(cond, j, e) do { if ((cond) && (j) >= 32 && (j) < 36) g_fwd_prof[((j) - 32) * 16 + (e)] = clock64(); } while (0)
+#else
+#define FWD_STAMP(cond, j, e) do { } while (0)
+#endif
+
 template <int D>
 struct FwdSmem {
   static constexpr int Q_BYTES = FA_BQ * D * 2;
   static constexpr int KV_BYTES = FA_BK * D * 2;
   static constexpr int K_OFF = Q_BYTES;
-  static constexpr int V_OFF = K_OFF + FA_STAGES * KV_BYTES;
-  static constexpr int BAR_OFF = V_OFF + FA_STAGES * KV_BYTES;
+  static constexpr int V_OFF = K_OFF + FA_KSTAGES * KV_BYTES;
+  static constexpr int BAR_OFF = V_OFF + FA_VSTAGES * KV_BYTES;
   static constexpr int XCH_OFF = BAR_OFF + 256;            // [2 tiles][2 halves][128 rows] fp32 row-max exchange
   static constexpr int TOTAL = XCH_OFF + 2048 + 1024;
 };
@@ -94,19 +105,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   const int bx = (int)blockIdx.x - p.n_copy;
   constexpr int DH = D / 64;                // 64-wide halves of the head dimension
-  constexpr uint32_t TMEM_COLS = 256;
+  // tensor memory: S (128 fp32 columns) | O (D columns) | P (bf16, 64 columns).  P has columns of its own, so the next
+  // score tile is computed while the warps still work on the current one.
+  constexpr uint32_t TMEM_COLS = (D == 64) ? 256 : 512;
   constexpr uint32_t O_COL = 128;
+  constexpr uint32_t P_COL = 128 + D;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + L::BAR_OFF);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;              // [2]
-  uint64_t* v_full = bars + 3;              // [2]
-  uint64_t* kv_empty = bars + 5;            // [2]
-  uint64_t* s_full = bars + 7;
-  uint64_t* p_full = bars + 8;
-  uint64_t* o_done = bars + 9;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+  uint64_t* k_full = bars + 1;              // [3]
+  uint64_t* k_empty = bars + 4;             // [3]
+  uint64_t* v_full = bars + 7;              // [2]
+  uint64_t* v_empty = bars + 9;             // [2]
+  uint64_t* s_full = bars + 11;
+  uint64_t* p_full = bars + 12;
+  uint64_t* o_done = bars + 13;
+  uint64_t* s_consumed = bars + 14;
+  uint64_t* pv_done = bars + 15;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 16);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -137,10 +154,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < FA_KSTAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < FA_VSTAGES; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     mbar_init(s_full, 1);
     mbar_init(p_full, 256);
     mbar_init(o_done, 1);
+    mbar_init(s_consumed, 8);
+    mbar_init(pv_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -159,9 +179,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int h = 0; h < DH; ++h) tma_load_4d(smem + h * (FA_BQ * 128), &tmQ, q_full, h * 64, hq, q0, b);
       int ready_block = -1;
       for (int j = 0; j < n_kv; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, p.status, 500)) break;
+        const int ks = j % FA_KSTAGES, vs = j % FA_VSTAGES;
+        if (!mbar_wait(&k_empty[ks], ((j / FA_KSTAGES) & 1) ^ 1, abort_flag, p.status, 500)) break;
         const int jj = j + j_start;
         const int k0 = (jj >= n_kv ? jj - n_kv : jj) * FA_BK;
         if (p.ready != nullptr) {
@@ -174,14 +193,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
           if (*abort_flag) break;
         }
-        uint8_t* sk = smem + L::K_OFF + st * L::KV_BYTES;
-        uint8_t* sv = smem + L::V_OFF + st * L::KV_BYTES;
-        mbar_expect_tx(&k_full[st], L::KV_BYTES);
+        uint8_t* sk = smem + L::K_OFF + ks * L::KV_BYTES;
+        uint8_t* sv = smem + L::V_OFF + vs * L::KV_BYTES;
+        mbar_expect_tx(&k_full[ks], L::KV_BYTES);
 #pragma unroll
-        for (int h = 0; h < DH; ++h) tma_load_4d(sk + h * (FA_BK * 128), &tmK, &k_full[st], h * 64, hkv, k0, b);
-        mbar_expect_tx(&v_full[st], L::KV_BYTES);
+        for (int h = 0; h < DH; ++h) tma_load_4d(sk + h * (FA_BK * 128), &tmK, &k_full[ks], h * 64, hkv, k0, b);
+        if (!mbar_wait(&v_empty[vs], ((j / FA_VSTAGES) & 1) ^ 1, abort_flag, p.status, 502)) break;
+        mbar_expect_tx(&v_full[vs], L::KV_BYTES);
 #pragma unroll
-        for (int h = 0; h < DH; ++h) tma_load_4d(sv + h * (FA_BK * 128), &tmV, &v_full[st], h * 64, hkv, k0, b);
+        for (int h = 0; h < DH; ++h) tma_load_4d(sv + h * (FA_BK * 128), &tmV, &v_full[vs], h * 64, hkv, k0, b);
       }
     }
   } else if (warp == 1) {
@@ -189,6 +209,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // The whole warp runs this code convergently and only the elected lane issues: the descriptors then stay
     // warp-uniform, and stepping one is a single add (see sdesc_at).
     if (n_kv > 0) {
+      const bool mprof = (bx == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0);
       const uint32_t leader = elect_one() ? 1u : 0u;
       constexpr uint32_t idesc_qk = make_idesc_bf16(FA_BQ, FA_BK, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(FA_BQ, D, false, true);
@@ -197,8 +218,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const SDesc dv0 = sdesc_split(make_sdesc(smem_u32(smem + L::V_OFF), FA_BK * 128, 1024));           // V tile, N-major
       const uint32_t s_tmem = tmem_base;
       const uint32_t o_tmem = tmem_base + O_COL;
+      const uint32_t p_tmem = tmem_base + P_COL;
       auto issue_qk = [&](int j) {
-        const SDesc dk = SDesc{dk0.lo + (uint32_t)(j & 1) * (L::KV_BYTES >> 4), dk0.hi};
+        const SDesc dk = SDesc{dk0.lo + (uint32_t)(j % FA_KSTAGES) * (L::KV_BYTES >> 4), dk0.hi};
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k / 4) * (FA_BQ * 128) + (k % 4) * 32;
@@ -206,6 +228,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           else umma_ss_cp<true>(leader, s_tmem, sdesc_at(dq, off), sdesc_at(dk, off), idesc_qk);
         }
         umma_commit_p(leader, s_full);
+        umma_commit_p(leader, &k_empty[j % FA_KSTAGES]);
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 600) && mbar_wait(&k_full[0], 0, abort_flag, p.status, 601);
       ok = __all_sync(0xffffffffu, ok);
@@ -213,24 +236,30 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_after();
         issue_qk(0);
         for (int j = 0; j < n_kv; ++j) {
-          const int st = j & 1;
-          bool w = mbar_wait(p_full, j & 1, abort_flag, p.status, 602) && mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag, p.status, 603);
+          const int st = j % FA_VSTAGES;
+          if (j + 1 < n_kv) {
+            // the warps hold S(j) in registers: the next score tile can be computed while they work on it
+            bool w0 = mbar_wait(s_consumed, j & 1, abort_flag, p.status, 605) && mbar_wait(&k_full[(j + 1) % FA_KSTAGES], ((j + 1) / FA_KSTAGES) & 1, abort_flag, p.status, 604);
+            if (!__all_sync(0xffffffffu, w0)) break;
+            tc_fence_after();
+            FWD_STAMP(mprof, j, 2);
+            issue_qk(j + 1);
+            FWD_STAMP(mprof, j, 3);
+          }
+          bool w = mbar_wait(p_full, j & 1, abort_flag, p.status, 602) && mbar_wait(&v_full[st], (j / FA_VSTAGES) & 1, abort_flag, p.status, 603);
           if (!__all_sync(0xffffffffu, w)) break;
           tc_fence_after();
+          FWD_STAMP(mprof, j, 0);
           const SDesc dv = SDesc{dv0.lo + (uint32_t)st * (L::KV_BYTES >> 4), dv0.hi};
           // A = P (bf16, 8 tensor-memory columns per 16 keys); B = V tile, N-major: 16 key rows = 2 KB
-          umma_ts_p(leader, o_tmem, s_tmem, sdesc_at(dv, 0), idesc_pv, j != 0);
+          umma_ts_p(leader, o_tmem, p_tmem, sdesc_at(dv, 0), idesc_pv, j != 0);
 #pragma unroll
           for (int k = 1; k < FA_BK / 16; ++k)
-            umma_ts_cp<true>(leader, o_tmem, s_tmem + (k >> 2) * 64 + (k & 3) * 8, sdesc_at(dv, k * 2048), idesc_pv);
-          umma_commit_p(leader, &kv_empty[st]);
-          if (j + 1 < n_kv) {
-            if (!__all_sync(0xffffffffu, mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 604))) break;
-            tc_fence_after();
-            issue_qk(j + 1);
-          } else {
-            umma_commit_p(leader, o_done);
-          }
+            umma_ts_cp<true>(leader, o_tmem, p_tmem + k * 8, sdesc_at(dv, k * 2048), idesc_pv);
+          umma_commit_p(leader, &v_empty[st]);
+          umma_commit_p(leader, pv_done);
+          FWD_STAMP(mprof, j, 1);
+          if (j + 1 == n_kv) umma_commit_p(leader, o_done);
         }
       }
     }
@@ -248,11 +277,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float m_used = -INFINITY;    // running max (scaled, log2 domain) the accumulators are relative to
     float l = 0.f;               // this thread's share of the row sum
     bool alive = n_kv > 0;
+    const bool wprof = (bx == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64);
     for (int j = 0; j < n_kv && alive; ++j) {
+      FWD_STAMP(wprof, j, 4);
       bool ok = mbar_wait(s_full, j & 1, abort_flag, p.status, 700);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { alive = false; break; }
       tc_fence_after();
+      FWD_STAMP(wprof, j, 5);
       const int jj = j + j_start;
       const int k0 = (jj >= n_kv ? jj - n_kv : jj) * FA_BK;
       const bool need_mask = (k0 + FA_BK > p.Tk) || (p.causal && (k0 + FA_BK - 1 + p.k_off > qpos_min));
@@ -263,6 +295,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) tmem_ld16(t_lane + cbase + 16 * ch, sv[ch]);
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive_warp(s_consumed);                     // S(j) is in registers: the next score tile may overwrite it
+      FWD_STAMP(wprof, j, 6);
       float mx = -INFINITY;
       if (need_mask) {
 #pragma unroll
@@ -273,13 +308,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
-          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(sv[ch][i]));
+          for (int i = 0; i < 16; i += 2) mx = fmax3(mx, __uint_as_float(sv[ch][i]), __uint_as_float(sv[ch][i + 1]));
       }
       // row maximum over both halves: exchange through shared memory with the partner warp (same rows)
       float* slot = xch + (j & 1) * 256;
       slot[half * 128 + row] = mx;
       asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
       mx = fmaxf(mx, slot[(half ^ 1) * 128 + row]);
+      FWD_STAMP(wprof, j, 7);
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       // lazy rescale: keep the old reference maximum unless it fell behind by more than 2^8
       const bool need = (m_new > m_used + 8.f);
@@ -288,6 +324,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         alpha = (m_used == -INFINITY) ? 0.f : ex2f(m_used - m_new);
         m_used = m_new;
         l *= alpha;
+      }
+      if (j > 0) {
+        // PV(j-1) has read the previous P and finished updating O
+        bool okp = mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, 702);
+        okp = __all_sync(0xffffffffu, okp);
+        if (!okp) { alive = false; break; }
+        tc_fence_after();
       }
       if (j > 0 && __any_sync(0xffffffffu, need)) {
         // each thread of the pair rescales its own half of the O columns
@@ -301,7 +344,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st32(t_lane + O_COL + c, v);
         }
       }
-      // p = exp2(s*scale - m); bf16 P (two per column) goes back into the first 32 columns of my own span
+      FWD_STAMP(wprof, j, 8);
+      // p = exp2(s*scale - m); bf16 P (two per column) goes into the P columns: k-step 4*half+ch at column (4*half+ch)*8
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
@@ -317,11 +361,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           l += p0 + p1;
           pk[i >> 1] = pack_bf16(p0, p1);
         }
-        tmem_st8(t_lane + cbase + ch * 8, pk);
+        tmem_st8(t_lane + P_COL + half * 32 + ch * 8, pk);
       }
+      FWD_STAMP(wprof, j, 9);
       tmem_wait_st();
       tc_fence_before();
+      FWD_STAMP(wprof, j, 10);
       mbar_arrive(p_full);
+      FWD_STAMP(wprof, j, 11);
     }
     // epilogue: O / l -> bf16, LSE
     if (alive) {
@@ -429,5 +476,23 @@ extern "C" int cpb_flash_fwd(const void* q, const void* k, const void* v, void* 
     if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::TOTAL)); cfg = true; }
     flash_fwd_kernel<128><<<grid, FA_THREADS, FwdSmem<128>::TOTAL, stream>>>(tq, tk, tv, p);
   }
+#ifdef CPB_FWD_PROF
+  {
+    long long h[64];
+    cudaStreamSynchronize(stream);
+    if (cudaMemcpyFromSymbol(h, g_fwd_prof, sizeof(h)) == cudaSuccess && h[4] != 0) {
+      static const char* names[12] = {"M:p_full+v_full", "M:PV issued", "M:k_full", "M:QK issued", "W:tile top", "W:s_full", "W:S loaded", "W:max exchanged",
+                                      "W:rescale done", "W:exp done", "W:P stored", "W:arrived"};
+      const long long base = h[4];
+      for (int t = 0; t < 4; ++t) {
+        int order[12]; for (int e = 0; e < 12; ++e) order[e] = e;
+        for (int a2 = 0; a2 < 12; ++a2) for (int b2 = a2 + 1; b2 < 12; ++b2) if (h[t * 16 + order[b2]] < h[t * 16 + order[a2]]) { int x = order[a2]; order[a2] = order[b2]; order[b2] = x; }
+        fprintf(stderr, "[flash_fwd prof D=%d] tile %d:", D, 32 + t);
+        for (int e = 0; e < 12; ++e) fprintf(stderr, " %s@%lld", names[order[e]], h[t * 16 + order[e]] - base);
+        fprintf(stderr, "\n");
+      }
+    }
+  }
+#endif
   return check_launch("flash_fwd");
 }

@@ -355,6 +355,11 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 #else
 #define CPB_MATH_ASM asm
 #endif
+__device__ __forceinline__ float fmax3(float a, float b, float c) {     // one instruction on sm_100
+  float r;
+  CPB_MATH_ASM("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 __device__ __forceinline__ float ex2f(float x) {
   float y;
   CPB_MATH_ASM("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -201,6 +201,35 @@ def test_flash_bwd(D, B, Tq, Tk, Hq, Hkv, causal):
     assert_close(dq.float(), wdq, cos=0.995, rel=5e-2, name="dq")
 
 
+@pytest.mark.parametrize("B,Tq,Tk,Hq,Hkv,causal", [(1, 512, 512, 4, 1, True), (2, 300, 712, 2, 2, False), (1, 2048, 2048, 8, 2, True)])
+def test_flash_bwd_d64_kernels_agree(B, Tq, Tk, Hq, Hkv, causal, monkeypatch):
+    """The head_dim-64 kernel (transposed, vectors folded into the MMAs) against the general kernel on the same inputs,
+    including the fp32-accumulating dK/dV mode; query positions of a zig-zag shard when causal."""
+    from context_parallelism_b200.ops import attention as A, attention_bwd as AB
+    from context_parallelism_b200.parallel.shard import local_positions
+    torch.manual_seed(11)
+    D = 64
+    q = torch.randn(B, Tq, Hq, D, device=dev()).bfloat16()
+    k = torch.randn(B, Tk, Hkv, D, device=dev()).bfloat16()
+    v = torch.randn(B, Tk, Hkv, D, device=dev()).bfloat16()
+    do = torch.randn(B, Tq, Hq, D, device=dev()).bfloat16()
+    scale = 1 / math.sqrt(D)
+    q_pos = None
+    if causal and Tq == 512:
+        q_pos = local_positions(4 * Tq, 4, 1, True).to(dev()).int()       # rank 1 of 4: chunks 1 and 6
+        k = torch.randn(B, 4 * Tq, Hkv, D, device=dev()).bfloat16()
+        v = torch.randn_like(k)
+    out, lse = A.flash_fwd(q, k, v, scale, causal, q_pos=q_pos)
+    got = {}
+    for general in (True, False):
+        monkeypatch.setattr(AB, "_USE_GENERAL_D64", general)
+        got[general] = A.flash_bwd(q, k, v, out, lse, do, scale, causal, q_pos=q_pos)
+        check_status()
+    for a, b_, n in zip(got[True], got[False], ("dq", "dk", "dv")):
+        assert torch.isfinite(b_.float()).all()
+        assert_close(b_.float(), a.float(), cos=0.9995, rel=3e-2, name=n)
+
+
 def test_flash_autograd_positions():
     from context_parallelism_b200.ops import attention as A
     from context_parallelism_b200.parallel.shard import local_positions
