@@ -104,6 +104,8 @@ def main() -> None:
     ap.add_argument("--T", type=int, default=131072)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--ulysses-size", type=int, default=0)
+    ap.add_argument("--cp", type=int, default=0, help="context-parallel degree (default: all GPUs); the rest is data parallel")
+    ap.add_argument("--yarn-scale", type=float, default=1.0, help="YaRN position-scaling factor (1 = plain RoPE)")
     ap.add_argument("--recompute", default="selective")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -132,14 +134,19 @@ def main() -> None:
     m = dict(MODELS[args.model])
     family = m.pop("family")
     mode = args.mode
-    usize = args.ulysses_size or (2 if (mode == "hybrid" and world % 2 == 0) else 1)
-    cfg = Config.from_env(family, world, env={}).replace(
-        **m, T=args.T, B=args.batch, cp_size=world, attn_mode=mode, rotator=args.rotator, ulysses_size=usize,
-        dtype="bf16", recompute=args.recompute, max_steps=1000, warmup_steps=10, global_batch=args.batch * args.T,
+    cp = args.cp or world
+    dp = world // cp
+    usize = args.ulysses_size or (2 if (mode == "hybrid" and cp % 2 == 0) else 1)
+    env = {"CP_SIZE": str(cp)}
+    if args.yarn_scale != 1.0:
+        env.update(YARN_SCALE=str(args.yarn_scale), YARN_ORIG_MAXPOS=str(args.T / args.yarn_scale))
+    cfg = Config.from_env(family, world, env=env).replace(
+        **m, T=args.T, B=args.batch, cp_size=cp, attn_mode=mode, rotator=args.rotator, ulysses_size=usize,
+        dtype="bf16", recompute=args.recompute, max_steps=1000, warmup_steps=10, global_batch=args.batch * args.T * dp,
         checkpointing=False)
     eng = TrainEngine(cfg, dev)
 
-    gen = torch.Generator().manual_seed(1234)           # same tokens on every rank (all CP ranks read the same batch)
+    gen = torch.Generator().manual_seed(1234 + eng.cp.dp_rank)   # all CP ranks of a replica read the same batch; replicas differ
     n_batches = 4
     host = [torch.randint(0, cfg.vocab_size, (args.batch, args.T + 1), generator=gen).pin_memory() for _ in range(n_batches)]
     devb = [h.to(dev) for h in host]
@@ -181,7 +188,7 @@ def main() -> None:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    tokens_per_step = args.batch * args.T
+    tokens_per_step = args.batch * args.T * dp
     value = tokens_per_step * args.steps / (ms / 1e3)
     final_loss = float(eng.global_loss(loss))
 
@@ -203,16 +210,18 @@ def main() -> None:
     # model FLOPs per step (whole job): dense matmuls 6*P_active*tokens + causal attention 3.5 * 2*T^2*d_attn*L
     p_dense = cfg.n_layer * (cfg.n_embd * (cfg.n_head + 2 * cfg.n_kv_head) * cfg.head_dim + cfg.n_head * cfg.head_dim * cfg.n_embd
                              + (3 if family == "llama" else 2) * cfg.n_embd * cfg.ffn_hidden) + cfg.n_embd * cfg.vocab_size
-    attn_flops = 3.5 * 2.0 * args.T * args.T * cfg.n_head * cfg.head_dim * cfg.n_layer * args.batch
+    attn_flops = 3.5 * 2.0 * args.T * args.T * cfg.n_head * cfg.head_dim * cfg.n_layer * args.batch * dp
     flops = 6.0 * p_dense * tokens_per_step + attn_flops
     if rank == 0:
-        par = "single" if world == 1 else (f"{mode}{world}" if mode != "hybrid" else f"hybrid_r{world // usize}xu{usize}")
+        par = "single" if world == 1 else (f"{mode}{cp}" if mode != "hybrid" else f"hybrid_r{cp // usize}xu{usize}")
+        if dp > 1:
+            par += f"xdp{dp}"
         print(json.dumps({
             "metric": f"training tokens/sec/box at T={args.T} ({mode} CP, {args.model})",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
-            "config": {"model": args.model, "global_batch": args.batch, "seq_len": args.T,
+            "config": {"model": args.model, "global_batch": args.batch * dp, "seq_len": args.T, "yarn_scale": args.yarn_scale,
                        "parallelism": par, "rotator": args.rotator if world > 1 else "none",
                        "recompute": args.recompute, "l2": "inputs larger than L2 (activations are GBs per layer)",
                        "optimizer_step_in_timed_region": True},
