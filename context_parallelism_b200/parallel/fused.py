@@ -30,7 +30,7 @@ from .. import _native as nv
 from ..ops import attention as A
 from ..ops import attention_bwd as AB
 from ..ops import permute
-from .symm import SymmetricHeap
+from .symm import SymmetricHeap, tensor_from_ptr
 
 N_COPY_CTAS = 16
 FLAG_BYTES = 4096
@@ -414,7 +414,10 @@ class _FusedSeqToHeadFn(torch.autograd.Function):
         _a2a_push(fc, g, [(q, ub.nq, 1, 0), (k, ub.kvl, ub.rep, ub.nq), (v, ub.kvl, ub.rep, ub.nq + ub.kvl)],
                   B, Tl, D, ub.hl, ub.qkv_off + slot * ub.qkv_bytes)
         fc.barrier(g)
-        land = ub.qkv_view(fc, slot)
+        # a tensor object of its own over the landing buffer: views of the shared arena tensor would share its version
+        # counter, and any later in-place copy into the arena would invalidate them for autograd
+        base = fc.heap.base + ub.qkv_off + slot * ub.qkv_bytes
+        land = tensor_from_ptr(base, ub.qkv_bytes, fc.device).view(torch.bfloat16).view(ub.B, ub.T, ub.hl, ub.D)
         ctx.fc, ctx.ub = fc, ub
         return land[:, :, :ub.nq], land[:, :, ub.nq:ub.nq + ub.kvl], land[:, :, ub.nq + ub.kvl:]
 
@@ -456,7 +459,7 @@ class _FusedHeadToSeqFn(torch.autograd.Function):
         do = do.contiguous()
         _a2a_push(fc, g, [(do, ub.nq, 1, 0)], ub.B, ub.Tl, ub.D, ub.nq, ub.do_off)
         fc.barrier(g)
-        return ub.do, None, None
+        return tensor_from_ptr(fc.heap.base + ub.do_off, ub.do.numel() * 2, fc.device).view(torch.bfloat16).view(ub.do.shape), None, None
 
 
 def fused_seq_to_head(fc: FusedComm, q, k, v):

@@ -24,6 +24,18 @@ def test_ring_fused_gpt2_recompute_2gpu():
                "--recompute", "selective", device="cuda")
 
 
+def test_hybrid_fused_ulysses_exchange_2gpu(monkeypatch):
+    """Hybrid with Ulysses degree 2 and ring degree 1: the peer-memory sequence<->head exchange around the local attention."""
+    monkeypatch.setenv("CP_FUSED_HYBRID_ULYSSES", "1")
+    run_worker(2, "--mode", "hybrid", "--ulysses", 2, "--rotator", "fused", "--T", 1024, "--tol", 3e-2, device="cuda")
+
+
+@pytest.mark.skipif(NGPU < 4, reason="needs 4 GPUs")
+def test_hybrid_fused_ulysses_exchange_4gpu(monkeypatch):
+    monkeypatch.setenv("CP_FUSED_HYBRID_ULYSSES", "1")
+    run_worker(4, "--mode", "hybrid", "--ulysses", 2, "--rotator", "fused", "--T", 2048, "--tol", 3e-2, device="cuda")
+
+
 @pytest.mark.skipif(NGPU < 4, reason="needs 4 GPUs")
 @pytest.mark.parametrize("mode,extra", [("ring", []), ("ulysses", ["--kv", 2]), ("hybrid", ["--ulysses", 2]),
                                         ("ring", ["--cp", 2])])
