@@ -15,10 +15,12 @@
 //     dV += P^T dO  (A in tensor memory)    dK += dS^T Q  (A in tensor memory)
 //     dQ  = dS K    (A = dS^T staged M-major in shared memory) -> TMA reduce-add into the fp32 dQ buffer.
 //
-// Issue order of the MMA thread (tile i = one 128x128 query/key tile pair):
+// Issue order of the MMA warp (tile i = one 128x128 query/key tile pair):
 //     S'(i+1) as soon as the warps have read S'(i);   then after the warps finish tile i:
-//     dV(i), dK(i), dQ(i), dP'(i+1)
-// so the exponentials of tile i+1 overlap the gradient products of tile i.  Tensor memory (512 columns):
+//     dK(i), dP'(i+1), dV(i), dQ(i)
+// so the exponentials of tile i+1 overlap the gradient products of tile i, and dP'(i+1) is ready long before the
+// warps want it.  The warps keep P^T and dS^T in registers until dQ(i-1) has finished and store them at the end of
+// the tile: two barrier waits in the middle of a tile, one at its end.  Tensor memory (512 columns):
 // S'^T 128 | dP'^T 128 (dS^T bf16 written back into it) | dV 64 | dK 64 | dQ 64 | P^T 64.
 //
 // Same interface, masking rules, dK/dV output modes and bounded waits as the general kernel.
@@ -37,7 +39,7 @@ namespace cpb {
 #else
 #define B64_PROF_ON(x) false
 #endif
-// diagnostic timeline: CTA (0,0,0), tiles 64..71: event e of tile t -> prof[16 + (t-64)*16 + e]
+// diagnostic timeline: CTA (0,0,0), tiles 64..71: event e of tile t -> prof[16 + (t-64)*32 + e]
 #define B64_STAMP(cond, t, e) do { if ((cond) && (t) >= 64 && (t) < 72) p.prof[16 + ((t) - 64) * 32 + (e)] = clock64(); } while (0)
 
 constexpr int B64_T = 128;
@@ -59,7 +61,6 @@ struct Bwd64Params {
   const uint64_t* route_v;
   int route_rows, route_tl;
   int debug_skip_dq;
-  int group_prof;
   long long* prof;              // diagnostic: CTA (0,0,0) writes cycle breakdowns here (16 counters)
   int* status;
 };
@@ -129,7 +130,6 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* dq_full = bars + 12;
   uint64_t* dq_empty = bars + 13;
   uint64_t* acc_done = bars + 14;
-  uint64_t* prof_bar = bars + 15;
   uint32_t* tmem_slot = (uint32_t*)(bars + 16);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* qt_start_s = (int*)(tmem_slot + 2);
@@ -144,7 +144,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(kv_full, 1);
     for (int s = 0; s < NST; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     mbar_init(s_ready, 1); mbar_init(s_consumed, 8); mbar_init(dp_ready, 1);
-    mbar_init(p_full, 8); mbar_init(dq_full, 1); mbar_init(dq_empty, 4); mbar_init(acc_done, 1); mbar_init(prof_bar, 1);
+    mbar_init(p_full, 8); mbar_init(dq_full, 1); mbar_init(dq_empty, 4); mbar_init(acc_done, 1);
     *abort_flag = 0;
     *qt_start_s = num_q_tiles;
     fence_mbar_init();
@@ -590,7 +590,6 @@ extern "C" int cpb_flash_bwd64(const void* q, const void* k, const void* v, cons
   const char* e = getenv("CPB_BWD_SKIP_DQ");
   p.debug_skip_dq = (e != nullptr && e[0] == '1');
   p.prof = nullptr;
-  { const char* ge = getenv("CPB_BWD_GROUP_PROF"); p.group_prof = (ge != nullptr && ge[0] == '1'); }
   const char* pe = getenv("CPB_BWD_PROF");
   if (pe != nullptr && pe[0] == '1') {
     void* sym = nullptr;
