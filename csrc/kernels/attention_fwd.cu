@@ -347,22 +347,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       FWD_STAMP(wprof, j, 8);
       // p = exp2(s*scale - m); bf16 P (two per column) goes into the P columns: k-step 4*half+ch at column (4*half+ch)*8
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+      // two copies of the loop: the common one (no tile edge, not on the diagonal) carries no compare/select per element
+      float l0 = 0.f, l1 = 0.f;
+      if (!need_mask) {
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t pk[8];
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t pk[8];
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          float p0 = ex2f(fmaf(__uint_as_float(sv[ch][i]), p.scale_log2, -m_sub));
-          float p1 = ex2f(fmaf(__uint_as_float(sv[ch][i + 1]), p.scale_log2, -m_sub));
-          if (need_mask) {
-            if (ch * 16 + i > kmax) p0 = 0.f;
-            if (ch * 16 + i + 1 > kmax) p1 = 0.f;
+          for (int i = 0; i < 16; i += 2) {
+            const float p0 = ex2f(fmaf(__uint_as_float(sv[ch][i]), p.scale_log2, -m_sub));
+            const float p1 = ex2f(fmaf(__uint_as_float(sv[ch][i + 1]), p.scale_log2, -m_sub));
+            l0 += p0; l1 += p1;
+            pk[i >> 1] = pack_bf16(p0, p1);
           }
-          l += p0 + p1;
-          pk[i >> 1] = pack_bf16(p0, p1);
+          tmem_st8(t_lane + P_COL + half * 32 + ch * 8, pk);
         }
-        tmem_st8(t_lane + P_COL + half * 32 + ch * 8, pk);
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t pk[8];
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const float p0 = (ch * 16 + i > kmax) ? 0.f : ex2f(fmaf(__uint_as_float(sv[ch][i]), p.scale_log2, -m_sub));
+            const float p1 = (ch * 16 + i + 1 > kmax) ? 0.f : ex2f(fmaf(__uint_as_float(sv[ch][i + 1]), p.scale_log2, -m_sub));
+            l0 += p0; l1 += p1;
+            pk[i >> 1] = pack_bf16(p0, p1);
+          }
+          tmem_st8(t_lane + P_COL + half * 32 + ch * 8, pk);
+        }
       }
+      l += l0 + l1;
       FWD_STAMP(wprof, j, 9);
       tmem_wait_st();
       tc_fence_before();
