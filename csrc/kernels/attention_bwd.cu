@@ -26,6 +26,7 @@
 // row, 64 key columns each, so every scheduler has two such warps to hide tensor-memory and MUFU latency),
 // 10..13 = dQ drain warps (thread = query row).
 #include "common.cuh"
+#include <type_traits>
 #include "host_utils.h"
 
 #include <stdlib.h>
@@ -321,34 +322,39 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld16(t_lane + S_COL + cbase, sv[0]);
       tmem_ld16(t_lane + DP_COL + cbase, dpv[0]);
       tmem_wait_ld();
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        if (ch < 3) {
-          tmem_ld16(t_lane + S_COL + cbase + 16 * (ch + 1), sv[ch + 1]);
-          tmem_ld16(t_lane + DP_COL + cbase + 16 * (ch + 1), dpv[ch + 1]);
-        }
-        uint32_t pk[8], dk_[8];
-#pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-          float p0 = ex2f(fmaf(__uint_as_float(sv[ch][j]), p.scale_log2, -lse2_r));
-          float p1 = ex2f(fmaf(__uint_as_float(sv[ch][j + 1]), p.scale_log2, -lse2_r));
-          if (need_mask) {
-            if (ch * 16 + j > kmax) p0 = 0.f;
-            if (ch * 16 + j + 1 > kmax) p1 = 0.f;
+      // two copies of the loop: the common one (no tile edge, not on the diagonal) carries no compare/select per element
+      auto sweep = [&](auto masked_c) {
+        constexpr bool MASKED = decltype(masked_c)::value;
+  #pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          if (ch < 3) {
+            tmem_ld16(t_lane + S_COL + cbase + 16 * (ch + 1), sv[ch + 1]);
+            tmem_ld16(t_lane + DP_COL + cbase + 16 * (ch + 1), dpv[ch + 1]);
           }
-          const float e0 = p0 * (__uint_as_float(dpv[ch][j]) - delta_r);
-          const float e1 = p1 * (__uint_as_float(dpv[ch][j + 1]) - delta_r);
-          pk[j >> 1] = pack_bf16(p0, p1);
-          dk_[j >> 1] = pack_bf16(e0, e1);
+          uint32_t pk[8], dk_[8];
+  #pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            float p0 = ex2f(fmaf(__uint_as_float(sv[ch][j]), p.scale_log2, -lse2_r));
+            float p1 = ex2f(fmaf(__uint_as_float(sv[ch][j + 1]), p.scale_log2, -lse2_r));
+            if (MASKED) {
+              if (ch * 16 + j > kmax) p0 = 0.f;
+              if (ch * 16 + j + 1 > kmax) p1 = 0.f;
+            }
+            const float e0 = p0 * (__uint_as_float(dpv[ch][j]) - delta_r);
+            const float e1 = p1 * (__uint_as_float(dpv[ch][j + 1]) - delta_r);
+            pk[j >> 1] = pack_bf16(p0, p1);
+            dk_[j >> 1] = pack_bf16(e0, e1);
+          }
+          // row r of P and dS -> shared memory, 128B-swizzled: 16-byte chunk (col % 64) / 8 of this thread's 64-key
+          // group goes to chunk position (chunk ^ (r & 7)).
+          *(uint4*)(p_row + (((2 * ch) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *(uint4*)(p_row + (((2 * ch + 1) ^ (r & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          *(uint4*)(ds_row + (((2 * ch) ^ (r & 7)) << 4)) = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
+          *(uint4*)(ds_row + (((2 * ch + 1) ^ (r & 7)) << 4)) = make_uint4(dk_[4], dk_[5], dk_[6], dk_[7]);
+          if (ch < 3) tmem_wait_ld();
         }
-        // row r of P and dS -> shared memory, 128B-swizzled: 16-byte chunk (col % 64) / 8 of this thread's 64-key
-        // group goes to chunk position (chunk ^ (r & 7)).
-        *(uint4*)(p_row + (((2 * ch) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        *(uint4*)(p_row + (((2 * ch + 1) ^ (r & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-        *(uint4*)(ds_row + (((2 * ch) ^ (r & 7)) << 4)) = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
-        *(uint4*)(ds_row + (((2 * ch + 1) ^ (r & 7)) << 4)) = make_uint4(dk_[4], dk_[5], dk_[6], dk_[7]);
-        if (ch < 3) tmem_wait_ld();
-      }
+      };
+      if (need_mask) sweep(std::true_type{}); else sweep(std::false_type{});
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive_warp(p_full);
