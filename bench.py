@@ -25,7 +25,7 @@ import sys
 import threading
 import time
 
-REF_UNAVAILABLE = ("reference is not installable: /root/reference has no setup.py/pyproject.toml and its Makefile needs the "
+REF_UNAVAILABLE = ("reference is not installable: its source tree has no setup.py/pyproject.toml and its Makefile needs the "
                    "absent BluTrain tensor library, MPI and mpic++")
 
 MODELS = {
