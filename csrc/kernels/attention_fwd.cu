@@ -350,18 +350,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // two copies of the loop: the common one (no tile edge, not on the diagonal) carries no compare/select per element
       float l0 = 0.f, l1 = 0.f;
       if (!need_mask) {
+        const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), m2 = pack_f32x2(-m_sub, -m_sub);
+        uint64_t l2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           uint32_t pk[8];
 #pragma unroll
           for (int i = 0; i < 16; i += 2) {
-            const float p0 = ex2f(fmaf(__uint_as_float(sv[ch][i]), p.scale_log2, -m_sub));
-            const float p1 = ex2f(fmaf(__uint_as_float(sv[ch][i + 1]), p.scale_log2, -m_sub));
-            l0 += p0; l1 += p1;
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[ch][i]), __uint_as_float(sv[ch][i + 1])), c2, m2), x0, x1);
+            const float p0 = ex2f(x0), p1 = ex2f(x1);
+            l2 = add_f32x2(l2, pack_f32x2(p0, p1));
             pk[i >> 1] = pack_bf16(p0, p1);
           }
           tmem_st8(t_lane + P_COL + half * 32 + ch * 8, pk);
         }
+        unpack_f32x2(l2, l0, l1);
       } else {
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
