@@ -72,13 +72,16 @@ class GPT2(nn.Module):
         self.attn = CPAttention(cfg, self.cp)
 
     def named_tensors(self) -> Dict[str, torch.Tensor]:
+        """Parameters under the names of the named-init files: each block's first LayerNorm lives inside its
+        attention module and the second inside its MLP (``transformer.h.<i>.attn.ln.*`` / ``.mlp.ln.*``,
+        Scripts/Blutrain/gpt2_cp_test.cpp:909-929; Scripts/Pytorch/gpt2_cp_attnstyle_fp32.py:192,300)."""
         out: Dict[str, torch.Tensor] = {"transformer.wte.weight": self.wte, "transformer.wpe.weight": self.wpe}
         for i, b in enumerate(self.blocks):
             p = f"transformer.h.{i}."
-            out[p + "ln_1.weight"], out[p + "ln_1.bias"] = b.ln_1_w, b.ln_1_b
+            out[p + "attn.ln.weight"], out[p + "attn.ln.bias"] = b.ln_1_w, b.ln_1_b
             out[p + "attn.c_attn.weight"], out[p + "attn.c_attn.bias"] = b.c_attn_w, b.c_attn_b
             out[p + "attn.c_proj.weight"], out[p + "attn.c_proj.bias"] = b.attn_proj_w, b.attn_proj_b
-            out[p + "ln_2.weight"], out[p + "ln_2.bias"] = b.ln_2_w, b.ln_2_b
+            out[p + "mlp.ln.weight"], out[p + "mlp.ln.bias"] = b.ln_2_w, b.ln_2_b
             out[p + "mlp.c_fc.weight"], out[p + "mlp.c_fc.bias"] = b.c_fc_w, b.c_fc_b
             out[p + "mlp.c_proj.weight"], out[p + "mlp.c_proj.bias"] = b.mlp_proj_w, b.mlp_proj_b
         out["transformer.ln_f.weight"], out["transformer.ln_f.bias"] = self.ln_f_w, self.ln_f_b

@@ -83,7 +83,7 @@ def main() -> None:
     M.log("GPT-2 CP trainer\n" + cfg.describe())
     eng = TrainEngine(cfg, dev)
     if cfg.load_init_named:
-        n = ckpt_mod.load_named_into(eng.model, eng.flat, ckpt_mod.read_named(cfg.load_init_named), strict=False)
+        n = ckpt_mod.load_named_into(eng.model, eng.flat, ckpt_mod.read_named(cfg.load_init_named), strict=True)
         M.log(f"loaded {n} named tensors from {cfg.load_init_named}")
     if cfg.save_init_named and rank == 0:
         n = ckpt_mod.save_named_init(cfg.save_init_named, eng.model, eng.flat)

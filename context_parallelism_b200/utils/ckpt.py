@@ -7,11 +7,12 @@ repeated ``int32 name_len | name bytes | int32 ndim | int64 dims[ndim] | float32
 
 Checkpoints reuse the same record stream: the model tensors under their reference names, then
 ``opt.m.<name>`` / ``opt.v.<name>`` Adam moments, then a ``__meta__`` record ``[step, loss, run]``.  Files are
-``<dir>/<prefix>_run<N>/<prefix>_run<N>_step_<S>.ckpt``; rank 0 saves, every rank loads, the newest
-``keep`` files are kept, and the run to resume is chosen like the reference does
-(Scripts/Blutrain/bluscriptCP.cpp:1049-1088): ``CP_CKPT_RESUME=<N>`` forces a run, ``CP_CKPT_NEW_RUN=1``
-forces a fresh one, otherwise the highest run whose last step is below ``max_steps``.  Checkpoints do not
-depend on sequence length or world size.
+``<dir>/<prefix>_run<N>_step_<S>.ckpt`` directly inside the checkpoint directory; rank 0 saves, every rank
+loads, the newest ``keep`` files of a run are kept, and the run to resume is chosen like the reference does
+(Scripts/Blutrain/bluscriptCP.cpp:1049-1088): ``CP_CKPT_RESUME=<N>`` forces a run (a new one if it has no
+file), ``CP_CKPT_NEW_RUN=1`` forces a fresh one, otherwise ONLY the highest run number is looked at: it is
+resumed when its last step is below ``max_steps``, and a new run starts when it is complete (older
+incomplete runs are never picked up).  Checkpoints do not depend on sequence length or world size.
 """
 from __future__ import annotations
 
@@ -85,7 +86,15 @@ def save_named_init(path: str, model, flat) -> int:
 
 def load_named_into(model, flat, tensors: Dict[str, torch.Tensor], strict: bool = True) -> int:
     """Copy records into the fp32 masters (and refresh the bf16 compute copies).  Vocabulary rows beyond the
-    file's row count stay zero (padding)."""
+    file's row count stay zero (padding).  ``strict``: every model tensor must be in the file.  Either way a file
+    record that matches no model tensor is an error (optimiser ``opt.*`` and ``__meta__`` records excepted, and
+    ``lm_head.weight`` of an untied file loaded into a tied model): a silently skipped record leaves a parameter at
+    its initial value, which a name mismatch between writer and reader would otherwise hide."""
+    known = set(model.named_tensors())
+    stray = [k for k in tensors if k not in known and not k.startswith("opt.") and k != "__meta__"
+             and k not in ("lm_head.weight", "lm_head")]
+    if stray:
+        raise KeyError(f"weight file has records that match no model tensor: {stray[:6]}{' ...' if len(stray) > 6 else ''}")
     by_param = {id(p): (name, p) for name, p, _, _ in flat.entries}
     masters = flat.named_master()
     n = 0
@@ -116,52 +125,46 @@ def load_named_into(model, flat, tensors: Dict[str, torch.Tensor], strict: bool 
 
 
 # ------------------------------------------------------------------ run-numbered checkpoints
-_RUN_RE = re.compile(r"_run(\d+)$")
-_STEP_RE = re.compile(r"_step_(\d+)\.ckpt$")
 
 
 class CheckpointManager:
     def __init__(self, root: str, prefix: str, keep: int = 6, rank: int = 0):
         self.root, self.prefix, self.keep, self.rank = root, prefix, keep, rank
         self.run: Optional[int] = None
-
-    def run_dir(self, run: int) -> str:
-        return os.path.join(self.root, f"{self.prefix}_run{run}")
+        self._file_re = re.compile(re.escape(prefix) + r"_run(\d+)_step_(\d+)\.ckpt$")
 
     def list_runs(self) -> Dict[int, List[int]]:
+        """``{run: sorted steps}`` from the flat ``<prefix>_run<K>_step_<S>.ckpt`` files of the directory."""
         runs: Dict[int, List[int]] = {}
         if not os.path.isdir(self.root):
             return runs
-        for d in os.listdir(self.root):
-            m = _RUN_RE.search(d)
-            if not m or not d.startswith(self.prefix):
-                continue
-            steps = []
-            for f in os.listdir(os.path.join(self.root, d)):
-                s = _STEP_RE.search(f)
-                if s:
-                    steps.append(int(s.group(1)))
-            runs[int(m.group(1))] = sorted(steps)
-        return runs
+        for f in os.listdir(self.root):
+            m = self._file_re.match(f)
+            if m and os.path.isfile(os.path.join(self.root, f)):
+                runs.setdefault(int(m.group(1)), []).append(int(m.group(2)))
+        return {r: sorted(s) for r, s in runs.items()}
 
     def resolve_run(self, max_steps: int, new_run: bool = False, resume: int = -1) -> Tuple[int, bool]:
         """Returns ``(run_number, resuming)``.  Call on rank 0 and broadcast the result."""
         runs = self.list_runs()
+        fresh = max(runs) + 1 if runs else 0
+        if new_run:
+            return fresh, False
         if resume >= 0:
-            return resume, bool(runs.get(resume))
-        if not new_run:
-            for r in sorted(runs, reverse=True):
-                if runs[r] and runs[r][-1] < max_steps:
-                    return r, True
-        return (max(runs) + 1 if runs else 0), False
+            return (resume, True) if runs.get(resume) else (fresh, False)
+        if runs:
+            last = max(runs)
+            if runs[last][-1] < max_steps:
+                return last, True
+        return fresh, False
 
     def path(self, run: int, step: int) -> str:
-        return os.path.join(self.run_dir(run), f"{self.prefix}_run{run}_step_{step}.ckpt")
+        return os.path.join(self.root, f"{self.prefix}_run{run}_step_{step}.ckpt")
 
     def save(self, run: int, step: int, model, flat, opt, loss: float) -> Optional[str]:
         if self.rank != 0:
             return None
-        os.makedirs(self.run_dir(run), exist_ok=True)
+        os.makedirs(self.root, exist_ok=True)
         recs = _split_fused(model, flat)
         for name, t in opt.state_dict().items():
             recs.append(("opt." + name, t))

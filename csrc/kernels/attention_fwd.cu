@@ -192,6 +192,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             ready_block = c;
           }
           if (*abort_flag) break;
+          // The copy CTAs wrote these rows with ordinary (generic-proxy) stores; the loads below go through the
+          // async proxy (TMA).  The acquire above orders generic accesses only, so a cross-proxy fence is needed
+          // before the first bulk-tensor read of a freshly arrived block.
+          asm volatile("fence.proxy.async.global;" ::: "memory");
         }
         uint8_t* sk = smem + L::K_OFF + ks * L::KV_BYTES;
         uint8_t* sv = smem + L::V_OFF + vs * L::KV_BYTES;

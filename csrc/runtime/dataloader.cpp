@@ -50,6 +50,18 @@ struct Loader {
     return CPB_OK;
   }
   int advance() { return open_shard((cur + 1) % shards.size()); }
+  // Make sure one batch (B*T+1 tokens) starting at this rank's position lies inside the current shard, moving on
+  // through at most every shard once.  A shard that is long enough for rank 0 may still be too short for a higher
+  // rank's start offset B*T*rank, so the check runs after every open, not only once per loader.
+  int ensure_batch() {
+    const size_t need = (size_t)B * T + 1;
+    for (size_t tries = 0; tries <= shards.size(); ++tries) {
+      if (pos + need <= tokens) return CPB_OK;
+      int rc = advance();
+      if (rc) return rc;
+    }
+    return set_error(CPB_ERR_ARG, "dataloader: no shard holds a batch of %d x %d tokens at rank %d of %d", B, T, rank, world);
+  }
 };
 }  // namespace
 
@@ -78,9 +90,8 @@ extern "C" int cpb_dl_shard(void* h) { return (int)((Loader*)h)->cur; }
 
 extern "C" int cpb_dl_next(void* h, int64_t* x, int64_t* y) {
   auto* L = (Loader*)h;
-  const size_t BT = (size_t)L->B * L->T, need = BT + 1;
-  if (L->tokens < need) return set_error(CPB_ERR_ARG, "dataloader: shard %s too small for one batch", L->shards[L->cur].c_str());
-  if (L->pos + need > L->tokens) { int rc = L->advance(); if (rc) return rc; }
+  const size_t BT = (size_t)L->B * L->T;
+  { int rc = L->ensure_batch(); if (rc) return rc; }
   const uint16_t* t = (const uint16_t*)L->map + L->pos;
   for (size_t i = 0; i < BT; ++i) { x[i] = t[i]; y[i] = t[i + 1]; }
   L->pos += BT * (size_t)L->world;
@@ -90,9 +101,9 @@ extern "C" int cpb_dl_next(void* h, int64_t* x, int64_t* y) {
 
 extern "C" int cpb_dl_skip(void* h, long n) {
   auto* L = (Loader*)h;
-  const size_t BT = (size_t)L->B * L->T, stride = BT * (size_t)L->world, need = BT + 1;
+  const size_t BT = (size_t)L->B * L->T, stride = BT * (size_t)L->world;
   for (long i = 0; i < n; ++i) {
-    if (L->pos + need > L->tokens) { int rc = L->advance(); if (rc) return rc; }
+    { int rc = L->ensure_batch(); if (rc) return rc; }
     L->pos += stride;
     if (L->pos + stride + 1 > L->tokens) { int rc = L->advance(); if (rc) return rc; }
   }

@@ -46,6 +46,15 @@ def test_named_init_roundtrip_and_names(tmp_path, family):
     else:
         assert names[0] == "transformer.wte.weight" and "transformer.h.1.attn.c_attn.weight" in names and names[-1] == "lm_head.weight"
         assert recs["transformer.h.0.attn.c_attn.weight"].shape == (96, 32)
+        # the complete name list of the reference's reader (Scripts/Blutrain/gpt2_cp_test.cpp:909-929)
+        per_layer = ["attn.ln.weight", "attn.ln.bias", "attn.c_attn.weight", "attn.c_attn.bias", "attn.c_proj.weight", "attn.c_proj.bias",
+                     "mlp.ln.weight", "mlp.ln.bias", "mlp.c_fc.weight", "mlp.c_fc.bias", "mlp.c_proj.weight", "mlp.c_proj.bias"]
+        n_layer = e1.cfg.n_layer
+        want = ["transformer.wte.weight", "transformer.wpe.weight"] + [f"transformer.h.{i}.{s}" for i in range(n_layer) for s in per_layer] \
+            + ["transformer.ln_f.weight", "transformer.ln_f.bias", "lm_head.weight"]
+        assert names == want
+        with pytest.raises(KeyError):
+            ckpt.load_named_into(e2.model, e2.flat, dict(recs, **{"transformer.h.0.ln_1.weight": recs["transformer.h.0.attn.ln.weight"]}))
     assert n == len(names)
     ckpt.load_named_into(e2.model, e2.flat, recs)
     assert torch.equal(e1.flat.master, e2.flat.master)
@@ -102,6 +111,15 @@ def test_shard_loader_schedule(tmp_path):
     assert torch.equal(x, x2)
     with pytest.raises(Exception):
         data.ShardLoader(str(tmp_path), "test", B, T)
+    # a shard long enough for rank 0 but shorter than a higher rank's start offset + one batch must be refused,
+    # not read past its end: the val shard has 300 tokens, rank 3 of 8 starts at 300
+    v0 = data.ShardLoader(str(tmp_path), "val", B, T, rank=0, world=8)
+    assert v0.next_batch()[0].shape == (B, T)
+    v3 = data.ShardLoader(str(tmp_path), "val", B, T, rank=3, world=8)
+    with pytest.raises(Exception, match="no shard holds a batch"):
+        v3.next_batch()
+    with pytest.raises(Exception, match="no shard holds a batch"):
+        v3.skip_batches(1)
     syn = data.SyntheticLoader(1000, 2, 16, seed=3)
     a, b = syn.next_batch()
     assert a.shape == (2, 16) and torch.equal(a[:, 1:], b[:, :-1]) and int(a.max()) < 1000

@@ -35,8 +35,7 @@ def test_llama_train_checkpoint_resume(tmp_path):
     env = {"CP_CKPT_DIR": tmp_path / "ck", "CP_LOG_DIR": tmp_path, "CP_CKPT_FREQ": "3", "CP_MAX_STEPS": "6", "CP_CKPT": "1"}
     out = run("context_parallelism_b200.trainers.llama_cp", dict(env, CP_MAX_STEPS="3"))
     assert "step     2" in out
-    run_dir = tmp_path / "ck" / "blumodelcp_run0"
-    assert (run_dir / "blumodelcp_run0_step_3.ckpt").exists()
+    assert (tmp_path / "ck" / "blumodelcp_run0_step_3.ckpt").exists()       # flat layout of the reference
     out2 = run("context_parallelism_b200.trainers.llama_cp", env)              # auto-resume run 0 at step 3
     assert "[resume] run 0 from step 3" in out2 and "step     5" in out2 and "step     2 " not in out2
     rows = list(csv.reader(open(tmp_path / "blumodelcp_run0_log.csv")))
@@ -51,7 +50,7 @@ def test_llama_train_checkpoint_resume(tmp_path):
     rows1 = [r for r in rows if r and r[0].isdigit()]
     assert abs(float(rows3[-1][1]) - float(rows1[-1][1])) < 1e-5
     out4 = run("context_parallelism_b200.trainers.llama_cp", dict(env, CP_CKPT_NEW_RUN="1", CP_MAX_STEPS="1"))
-    assert (tmp_path / "ck" / "blumodelcp_run1").exists()
+    assert (tmp_path / "ck" / "blumodelcp_run1_step_1.ckpt").exists()
 
 
 def test_eval_ppl_is_cp_invariant(tmp_path):
