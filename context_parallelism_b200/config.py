@@ -73,7 +73,8 @@ KNOWN_ENV = {
     # test only
     "CP_RING_SIZE", "CP_HYBRID_GQA",
     # this framework's additions
-    "CP_FUSED", "CP_WATCHDOG_S", "CP_NVLS", "CP_GRAD_BUCKET_MB", "CP_DKV_MODE",
+    "CP_FUSED", "CP_WATCHDOG_S", "CP_NVLS", "CP_GRAD_BUCKET_MB", "CP_DKV_MODE", "CP_SHARD_OPTIM", "CP_AR_CTAS",
+    "CP_FUSED_HYBRID_ULYSSES", "CP_LOAD_BALANCE", "CP_PHASE_TIMING",
 }
 
 
@@ -200,9 +201,11 @@ class Config:
     ring_bf16: bool = True
     save_kv_bf16: bool = True
     attn_fp32: bool = False
-    dkv_mode: str = "pull"              # pull (deterministic) | red (remote atomics)
+    dkv_mode: str = "route"             # route (red.add into the owner, fastest) | pull (deterministic, rank-ordered sum)
+    shard_optim: bool = True            # fused transport: reduce-scatter -> AdamW on the owned slice -> all-gather
+    load_balance_ring: bool = True      # HeadTail sharding on the ring axis; False = contiguous shards
     grad_bucket_mb: int = 25
-    nvls: bool = True
+    nvls: bool = False
     watchdog_s: float = 600.0
     # context extension
     yarn: YarnConfig = field(default_factory=YarnConfig)
@@ -263,8 +266,9 @@ class Config:
 
     @property
     def load_balance(self) -> bool:
-        """HeadTail is used on the ring axis (ring and hybrid); Ulysses shards contiguously."""
-        return self.attn_mode in ("ring", "hybrid")
+        """HeadTail is used on the ring axis (ring and hybrid) unless ``CP_LOAD_BALANCE=0``; Ulysses shards
+        contiguously."""
+        return self.attn_mode in ("ring", "hybrid") and self.load_balance_ring
 
     @property
     def t_local(self) -> int:
@@ -327,6 +331,21 @@ class Config:
             die("CP_CREAM_MODE requires CP_SIZE=1 (bluscriptCP.cpp:717-719)")
         if self.eval_ppl and self.dp_size != 1:
             die("CP_EVAL_PPL requires DP=1")
+        if self.dkv_mode not in ("route", "pull"):
+            die(f"CP_DKV_MODE={self.dkv_mode!r} must be route|red|pull")
+        if self.recompute not in ("none", "selective", "full"):
+            die(f"CP_RECOMPUTE={self.recompute!r} must be none|selective|full")
+        # knobs of the reference that have no counterpart here are refused loudly instead of being ignored
+        if self.nvls:
+            die("CP_NVLS=1 is not supported: the gradient reduction uses plain peer loads (no multimem / NVLS kernel is built)")
+        if self.debug.use_per_step_lse:
+            die("USE_PER_STEP_LSE=1 is not supported: the kernels keep one running (m, l, O) per row, there is no per-step LSE")
+        if self.dtype == "bf16" and not self.ring_bf16:
+            die("CP_RING_BF16=0 is not supported with CP_DTYPE=bf16: K/V travel in the compute dtype (fp32 transport is the CP_DTYPE=fp32 oracle path)")
+        if self.dtype == "bf16" and not self.save_kv_bf16:
+            die("CP_SAVE_KV_BF16=0 is not supported with CP_DTYPE=bf16: K/V are kept in the compute dtype")
+        if not self.load_balance_ring and self.attn_mode == "hybrid":
+            die("CP_LOAD_BALANCE=0 is supported in ring mode only")
 
     def describe(self) -> str:
         lines = []
@@ -354,9 +373,11 @@ def _common(env, world_size):
         ring_bf16=_flag(env, "CP_RING_BF16", True),
         save_kv_bf16=_flag(env, "CP_SAVE_KV_BF16", True),
         attn_fp32=_flag(env, "ATTN_FP32"),
-        dkv_mode=_str(env, "CP_DKV_MODE", "pull"),
+        dkv_mode={"red": "route"}.get(_str(env, "CP_DKV_MODE", "route").lower(), _str(env, "CP_DKV_MODE", "route").lower()),
+        shard_optim=_flag(env, "CP_SHARD_OPTIM", True),
+        load_balance_ring=_flag(env, "CP_LOAD_BALANCE", True),
         grad_bucket_mb=_int(env, "CP_GRAD_BUCKET_MB", 25),
-        nvls=_flag(env, "CP_NVLS", True),
+        nvls=_flag(env, "CP_NVLS", False),
         watchdog_s=_float(env, "CP_WATCHDOG_S", 600.0),
         data_root=_str(env, "CP_DATA_ROOT", ""),
         synthetic=_flag(env, "CP_SYNTHETIC") or not _str(env, "CP_DATA_ROOT", ""),

@@ -52,16 +52,20 @@ class TrainEngine:
         bf16 = cfg.dtype == "bf16" and device.type == "cuda"
         if device.type == "cuda" and not bf16:
             raise ValueError("the CUDA kernels compute in bf16; CP_DTYPE=fp32 is the CPU oracle path")
-        self.flat = FlatParams(self.model.named_parameters(), bf16)
+        if self.world > 1:
+            # every replica starts from rank 0's values (DDP ``init_sync``, bluscriptCP.cpp:1011)
+            with torch.no_grad():
+                for p in self.model.parameters():
+                    dist.broadcast(p.data, 0)
+        fused_world = self.cp.fused if (self.cp.fused is not None and self.cp.fused.covers_world()) else None
+        shard = fused_world if (cfg.shard_optim and not cfg.no_grad_allreduce) else None
+        self.flat = FlatParams(self.model.named_parameters(), bf16, cfg.grad_bucket_mb, shard)
         self.opt = AdamW(self.flat, cfg.max_lr, (cfg.beta1, cfg.beta2), cfg.adam_eps, cfg.weight_decay)
-        fused_ar = None
-        if self.cp.fused is not None and self.cp.fused.covers_world():
-            fused_ar = self.cp.fused.grad_allreduce_for(self.flat)
+        fused_ar = fused_world.grad_allreduce_for(self.flat) if fused_world is not None else None
         self.reducer = GradReducer(self.flat, None, self.world, cfg.grad_bucket_mb, fused_ar,
-                                   overlap=not cfg.debug.no_overlap)
+                                   overlap=not (cfg.debug.no_overlap or cfg.debug.no_overlap_bwd))
         if cfg.no_grad_allreduce:
             self.reducer.enabled = False
-        self.reducer.broadcast_params(0)
         self.step_idx = 0
         self.resume_anchor = -1
         self._pos_dev = {}
@@ -130,6 +134,16 @@ class TrainEngine:
     def eval_loss(self, tokens, targets) -> torch.Tensor:
         idx, tgt, pos = self.shard_batch(tokens, targets)
         return self.model.loss_sum(idx, tgt, pos, 0.0) / idx.numel()
+
+    def finish_step(self) -> None:
+        """Host-side end of a step's device work, called by the trainers before the optimiser runs: wait for the
+        stream with the ``CP_WATCHDOG_S`` deadline (a polling wait on a watched work handle, so a stuck collective
+        raises ``StepTimeout`` instead of hanging the job), then turn any bounded-wait expiry or bounds failure the
+        kernels reported into an exception, so that an update is never applied on top of stale data."""
+        if self.device.type == "cuda":
+            from .parallel.work import wait_for_stream
+            wait_for_stream(self.device, self.cfg.watchdog_s, f"step {self.step_idx}")
+        self.check_kernels()
 
     def check_kernels(self) -> None:
         """Raise if any kernel reported a bounded-wait expiry or a bounds failure (one small D2H read)."""

@@ -94,8 +94,11 @@ class GPT2(nn.Module):
         x = E.embedding(idx_local, self.wte, pos, self.wpe)
         pending = None
         use_ckpt = cfg.recompute in ("selective", "full") and torch.is_grad_enabled()
+        full = cfg.recompute == "full" and torch.is_grad_enabled()
         for blk in self.blocks:
-            if use_ckpt:
+            if full:
+                x, pending = checkpoint(self._block, blk, x, pending, pos, use_reentrant=False)
+            elif use_ckpt:
                 x, qkv = checkpoint(blk.pre_attention, x, pending, use_reentrant=False)
                 o = self.attn(qkv, pos)
                 x, pending = checkpoint(blk.post_attention, x, o, use_reentrant=False)
@@ -105,6 +108,12 @@ class GPT2(nn.Module):
                 x, pending = blk.post_attention(x, o)
         h, _ = E.layernorm(x, self.ln_f_w, self.ln_f_b, 1e-5, pending)
         return h
+
+    def _block(self, blk, x, pending, pos):
+        """One whole block; ``CP_RECOMPUTE=full`` re-runs it (attention and its communication included) in backward."""
+        x, qkv = blk.pre_attention(x, pending)
+        o = self.attn(qkv, pos)
+        return blk.post_attention(x, o)
 
     def head_weight(self) -> torch.Tensor:
         return self.wte if self.lm_head is None else self.lm_head

@@ -75,11 +75,13 @@ class Llama(nn.Module):
         self.cfg = cfg
         self.cp = cp or CPContext.single(cfg)
         gen = torch.Generator().manual_seed(cfg.seed if seed is None else seed)
-        self.wte = nn.Parameter(_padded_normal(cfg.vocab_size, cfg.vocab_padded, cfg.n_embd, gen))
-        self.blocks = nn.ModuleList([LlamaBlock(cfg, i, gen) for i in range(cfg.n_layer)])
+        # every tensor is drawn from the CPU generator (same values on every rank and on the CPU oracle) and moved to
+        # the device at once, so the host never holds more than one layer of an 8B-parameter model
+        self.wte = nn.Parameter(_padded_normal(cfg.vocab_size, cfg.vocab_padded, cfg.n_embd, gen).to(device))
+        self.blocks = nn.ModuleList([LlamaBlock(cfg, i, gen).to(device) for i in range(cfg.n_layer)])
         self.norm_f = nn.Parameter(torch.ones(cfg.n_embd))
         self.lm_head = None if cfg.weight_tying else nn.Parameter(
-            _padded_normal(cfg.vocab_size, cfg.vocab_padded, cfg.n_embd, gen))
+            _padded_normal(cfg.vocab_size, cfg.vocab_padded, cfg.n_embd, gen).to(device))
         self.to(device)
         self.attn = CPAttention(cfg, self.cp)
         self.rope_cache = R.build_rope_cache(cfg.T, cfg.head_dim, cfg.rope_theta, device, cfg.yarn)
@@ -124,8 +126,13 @@ class Llama(nn.Module):
         pending = None
         rpos = pos if self.rope_pos_override is None else self.rope_pos_override
         use_ckpt = cfg.recompute in ("selective", "full") and torch.is_grad_enabled()
+        full = cfg.recompute == "full" and torch.is_grad_enabled()
         for blk in self.blocks:
-            if use_ckpt:
+            if full:
+                # full activation recompute: only the block's input survives the forward pass; backward re-runs the
+                # whole block, context-parallel attention (and its communication) included, on every rank alike
+                x, pending = checkpoint(self._block, blk, x, pending, rpos, pos, use_reentrant=False)
+            elif use_ckpt:
                 x, qkv = checkpoint(blk.pre_attention, x, pending, self.rope_cache, rpos, use_reentrant=False)
                 o = self.attn(qkv, pos)
                 x, pending = checkpoint(blk.post_attention, x, o, use_reentrant=False)
@@ -135,6 +142,11 @@ class Llama(nn.Module):
                 x, pending = blk.post_attention(x, o)
         h, _ = E.rmsnorm(x, self.norm_f, cfg.rms_eps, pending)
         return h
+
+    def _block(self, blk, x, pending, rpos, pos):
+        x, qkv = blk.pre_attention(x, pending, self.rope_cache, rpos)
+        o = self.attn(qkv, pos)
+        return blk.post_attention(x, o)
 
     def head_weight(self) -> torch.Tensor:
         return self.wte if self.lm_head is None else self.lm_head

@@ -69,11 +69,12 @@ class CPContext:
             return torch.arange(T)
         if cfg.attn_mode == "hybrid":
             return shard.hybrid_local_positions(T, self.ring_size, self.ring_rank, self.ulysses_size, self.ulysses_rank)
-        return shard.local_positions(T, self.cp_size, self.cp_rank, cfg.attn_mode == "ring")
+        return shard.local_positions(T, self.cp_size, self.cp_rank, cfg.load_balance)
 
     def ring_positions(self, T: int) -> List[torch.Tensor]:
         """Position vectors of every ring rank's block (after the Ulysses combine in hybrid mode)."""
-        return [shard.local_positions(T, self.ring_size, s, True) for s in range(self.ring_size)]
+        lb = self.cfg.load_balance or self.cfg.attn_mode == "hybrid"
+        return [shard.local_positions(T, self.ring_size, s, lb) for s in range(self.ring_size)]
 
 
 class CPAttention:
@@ -81,6 +82,9 @@ class CPAttention:
         self.cfg, self.ctx = cfg, ctx
         self.scale = cfg.head_dim ** -0.5
         self._pos_cache = {}
+        from ..utils.debug import DebugTools
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        self.dbg = ctx.fused.dbg if ctx.fused is not None else DebugTools(cfg, rank)
 
     def _ring_pos(self, T: int, device):
         key = (T, str(device))
@@ -109,7 +113,9 @@ class CPAttention:
             else:
                 from .ring import ring_attention
                 kind = "p2p" if cfg.rotator == "fused" else cfg.rotator
-                o, _ = ring_attention(q, k, v, mypos, allp, ctx.ring_group, kind, self.scale, not cfg.recompute_k and False)
+                # the reference keeps the N-1 received K/V blocks for backward unless CP_RECOMPUTE_K asks to rotate
+                # them again (context_parallel/ContextParallelBackward.h:214-242)
+                o, _ = ring_attention(q, k, v, mypos, allp, ctx.ring_group, kind, self.scale, not cfg.recompute_k, self.dbg)
         elif mode == "ulysses":
             if fused:
                 o = ctx.fused.ulysses_attention(q, k, v, self.scale)

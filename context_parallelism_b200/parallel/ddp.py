@@ -12,7 +12,9 @@ Reduction is an AVERAGE over every rank of the group (all dp·cp ranks: each ran
 its own tokens, Scripts/Blutrain/gpt2_cp_test.cpp:1574-1601; context_parallel/RopeGammaAccum.h:16-21).
 
 Transports: ``nccl`` (``dist.all_reduce``; baseline, also used on gloo/CPU) or ``fused`` (the peer-memory
-all-reduce kernel of ``parallel.fused``: cast/scale + reduce in one pass over NVLink).
+kernels of ``parallel.fused``).  With the sharded optimiser (the default of the fused transport) a bucket is only
+reduce-scattered: every rank reduces the sub-slice it owns straight from the peers' fp32 gradient buffers, and its
+AdamW consumes that shard; with ``CP_SHARD_OPTIM=0`` the two-shot all-reduce (cast/scale + reduce + gather) runs.
 """
 from __future__ import annotations
 
@@ -30,20 +32,14 @@ class GradReducer:
         self.enabled = world > 1
         self.sync_enabled = True
         self.overlap = overlap and flat.device.type == "cuda"
-        cap = max(1, bucket_mb) * (1 << 20) // 4
-        # buckets are contiguous ranges of the flat buffer, cut at parameter boundaries
-        self.buckets: List[List[int]] = []          # [start, end, n_expected, n_seen]
+        # buckets are contiguous ranges of the flat buffer, cut at parameter boundaries (planned by FlatParams so the
+        # sharded optimiser and the reducer agree on them)
+        self.buckets: List[List[int]] = [[s, e] for s, e in flat.buckets]
         self.param_bucket: Dict[int, int] = {}
-        start = 0
-        cur_params = []
+        starts = [b[0] for b in self.buckets]
+        import bisect
         for name, p, off, n in flat.entries:
-            end = off + (n + 63) // 64 * 64
-            cur_params.append(p)
-            if end - start >= cap:
-                self._close_bucket(start, end, cur_params)
-                start, cur_params = end, []
-        if cur_params:
-            self._close_bucket(start, flat.total, cur_params)
+            self.param_bucket[id(p)] = bisect.bisect_right(starts, off) - 1
         self.expected: Optional[Dict[int, int]] = None      # hook invocations per parameter in one backward
         self._calls: Dict[int, int] = {}
         self._seen: List[int] = [0] * len(self.buckets)
@@ -53,12 +49,6 @@ class GradReducer:
         if self.enabled:
             for _, p, _, _ in flat.entries:
                 p._grad_ready = self._on_ready
-
-    def _close_bucket(self, start, end, params):
-        idx = len(self.buckets)
-        self.buckets.append([start, end])
-        for p in params:
-            self.param_bucket[id(p)] = idx
 
     @contextlib.contextmanager
     def no_sync(self):
@@ -101,12 +91,14 @@ class GradReducer:
         if self.stream is not None:
             self.stream.wait_stream(torch.cuda.current_stream(self.flat.device))
             with torch.cuda.stream(self.stream):
-                self._allreduce(buf, s)
+                self._allreduce(buf, s, b)
         else:
-            self._allreduce(buf, s)
+            self._allreduce(buf, s, b)
 
-    def _allreduce(self, buf: torch.Tensor, offset: int) -> None:
-        if self.fused is not None and buf.is_cuda:
+    def _allreduce(self, buf: torch.Tensor, offset: int, b: int) -> None:
+        if self.fused is not None and buf.is_cuda and self.flat.sharded:
+            self.fused.reduce_scatter_bucket(self.flat, b)       # the owner's AdamW consumes the reduced shard
+        elif self.fused is not None and buf.is_cuda:
             self.fused.allreduce_avg_(buf, offset)
         else:
             dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
@@ -135,6 +127,8 @@ class GradReducer:
         """Initial parameter sync from rank ``src`` of the group (DDP ``init_sync``, bluscriptCP.cpp:1011)."""
         if not self.enabled:
             return
+        if self.flat.sharded:
+            raise RuntimeError("broadcast_params: with a sharded optimiser broadcast the model parameters before packing them")
         ranks = dist.get_process_group_ranks(self.group) if self.group is not None else None
         gsrc = ranks[src] if ranks is not None else src
         dist.broadcast(self.flat.master, gsrc, group=self.group)

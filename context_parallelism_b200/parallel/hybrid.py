@@ -37,7 +37,7 @@ def hybrid_attention(q, k, v, ctx, attn, fused: bool):
         else:
             from .ring import ring_attention
             kind = "p2p" if attn.cfg.rotator == "fused" else attn.cfg.rotator
-            o, _ = ring_attention(q, k, v, mypos, allp, ctx.ring_group, kind, attn.scale, False)
+            o, _ = ring_attention(q, k, v, mypos, allp, ctx.ring_group, kind, attn.scale, not attn.cfg.recompute_k, attn.dbg)
     else:
         from ..ops import attention as A
         o, _ = A.flash_attention(q, k, v, attn.scale, True)

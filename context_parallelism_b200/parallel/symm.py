@@ -88,6 +88,17 @@ class SymmetricHeap:
         off = self.alloc(name, n * torch.empty((), dtype=dtype).element_size())
         return self.view(off, shape, dtype), off
 
+    def raw_tensor(self, name: str, shape, dtype: torch.dtype) -> Tuple[torch.Tensor, int]:
+        """Like :meth:`tensor`, but the result is a tensor object of its own over the arena memory (own storage
+        object, own autograd version counter): in-place writes elsewhere in the arena do not invalidate it for
+        autograd.  Used for buffers that parameters are views of."""
+        n = 1
+        for s in shape:
+            n *= s
+        nb = n * torch.empty((), dtype=dtype).element_size()
+        off = self.alloc(name, nb)
+        return tensor_from_ptr(self.base + off, nb, self.device).view(dtype).view(*shape), off
+
     def close(self) -> None:
         torch.cuda.synchronize(self.device)
         if dist.is_initialized():

@@ -94,6 +94,7 @@ def train(cfg: Config, eng: TrainEngine, impl: str, csv_header: str,
             with timers.phase("timer_fwd_bwd"):
                 loss_acc += eng.forward_backward(x, y, accum, last=(micro == accum - 1)).float() / accum
         lr = eng.lr_at(eng.step_idx)
+        eng.finish_step()          # bounded wait + kernel status: a failed step never reaches the optimiser
         with timers.phase("timer_optim"):
             norm = eng.optimizer_step()
         loss = float(eng.global_loss(loss_acc))

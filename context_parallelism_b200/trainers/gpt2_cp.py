@@ -59,6 +59,7 @@ def generate(eng: TrainEngine, prompt: torch.Tensor, n_new: int = 32, top_k: int
 def dump_step0_grads(eng: TrainEngine, path: str) -> None:
     """Per-parameter gradient L2 norms after the averaged all-reduce of the first step
     (gpt2_cp_test.cpp:1371-1487), as ``name,l2`` lines under the named-init names."""
+    grad = eng.flat.full_reduced_grad()         # collective when the optimiser state is sharded
     if eng.rank != 0:
         return
     by_param = {id(p): (o, n) for _, p, o, n in eng.flat.entries}
@@ -69,7 +70,7 @@ def dump_step0_grads(eng: TrainEngine, path: str) -> None:
             if id(base) not in by_param:
                 continue
             o, n = by_param[id(base)]
-            f.write(f"{name},{float(eng.flat.grad[o:o + n].norm()):.8e}\n")
+            f.write(f"{name},{float(grad[o:o + n].norm()):.8e}\n")
 
 
 def main() -> None:
@@ -85,8 +86,8 @@ def main() -> None:
     if cfg.load_init_named:
         n = ckpt_mod.load_named_into(eng.model, eng.flat, ckpt_mod.read_named(cfg.load_init_named), strict=True)
         M.log(f"loaded {n} named tensors from {cfg.load_init_named}")
-    if cfg.save_init_named and rank == 0:
-        n = ckpt_mod.save_named_init(cfg.save_init_named, eng.model, eng.flat)
+    if cfg.save_init_named:
+        n = ckpt_mod.save_named_init(cfg.save_init_named, eng.model, eng.flat, rank)
         M.log(f"saved {n} named tensors to {cfg.save_init_named}")
 
     def periodic(step: int) -> None:

@@ -182,9 +182,8 @@ def main() -> None:
             ckpt_mod.write_named(cfg.dump_rope, [("rope_cache", eng.model.rope_cache[:n])])
         M.log(f"[dump] rope cache rows={n} -> {cfg.dump_rope}")
     elif cfg.dump_named:
-        if rank == 0:
-            n = ckpt_mod.save_named_init(cfg.dump_named, eng.model, eng.flat)
-            M.log(f"[dump] {n} named tensors -> {cfg.dump_named}")
+        n = ckpt_mod.save_named_init(cfg.dump_named, eng.model, eng.flat, rank)
+        M.log(f"[dump] {n} named tensors -> {cfg.dump_named}")
     elif cfg.dump_acts:
         ld = data_mod.make_loader(cfg, "val", eng.cp.dp_rank, eng.cp.dp_size)
         x, y = ld.next_batch()

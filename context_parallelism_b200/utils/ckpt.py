@@ -80,8 +80,10 @@ def _split_fused(model, flat) -> List[Tuple[str, torch.Tensor]]:
     return out
 
 
-def save_named_init(path: str, model, flat) -> int:
-    return write_named(path, _split_fused(model, flat))
+def save_named_init(path: str, model, flat, rank: int = 0) -> int:
+    """Every rank calls this (collective when the optimiser state is sharded); rank 0 writes."""
+    recs = _split_fused(model, flat)
+    return write_named(path, recs) if rank == 0 else len(recs)
 
 
 def load_named_into(model, flat, tensors: Dict[str, torch.Tensor], strict: bool = True) -> int:
@@ -96,7 +98,6 @@ def load_named_into(model, flat, tensors: Dict[str, torch.Tensor], strict: bool 
     if stray:
         raise KeyError(f"weight file has records that match no model tensor: {stray[:6]}{' ...' if len(stray) > 6 else ''}")
     by_param = {id(p): (name, p) for name, p, _, _ in flat.entries}
-    masters = flat.named_master()
     n = 0
     for name, view in model.named_tensors().items():
         if name not in tensors:
@@ -108,17 +109,16 @@ def load_named_into(model, flat, tensors: Dict[str, torch.Tensor], strict: bool 
         ent = by_param.get(id(base))
         if ent is None:
             continue
-        m = masters[ent[0]]
+        row0 = 0
         if view._base is not None:
             off = view.storage_offset() - base.storage_offset()
-            rows = off // base.shape[1]
-            m = m[rows:rows + view.shape[0]]
-        if src.dim() == 2 and m.dim() == 2 and src.shape[0] < m.shape[0] and src.shape[1] == m.shape[1]:
-            m[: src.shape[0]].copy_(src)
-        else:
-            if tuple(src.shape) != tuple(m.shape):
-                raise ValueError(f"{name}: file shape {tuple(src.shape)} != model shape {tuple(m.shape)}")
-            m.copy_(src)
+            row0 = off // base.shape[1]
+        want = tuple(view.shape)
+        if src.dim() == 2 and len(want) == 2 and src.shape[0] < want[0] and src.shape[1] == want[1]:
+            pass                                   # fewer vocabulary rows than the padded table: the rest stays zero
+        elif tuple(src.shape) != want:
+            raise ValueError(f"{name}: file shape {tuple(src.shape)} != model shape {want}")
+        flat.load_master_rows(ent[0], row0, src)
         n += 1
     flat.sync_compute_copy()
     return n
@@ -162,11 +162,14 @@ class CheckpointManager:
         return os.path.join(self.root, f"{self.prefix}_run{run}_step_{step}.ckpt")
 
     def save(self, run: int, step: int, model, flat, opt, loss: float) -> Optional[str]:
+        """Every rank calls this (assembling the masters and moments of a sharded optimiser is a collective); rank 0
+        writes."""
+        recs = _split_fused(model, flat)
+        state = opt.state_dict()
         if self.rank != 0:
             return None
         os.makedirs(self.root, exist_ok=True)
-        recs = _split_fused(model, flat)
-        for name, t in opt.state_dict().items():
+        for name, t in state.items():
             recs.append(("opt." + name, t))
         recs.append(("__meta__", torch.tensor([float(step), float(loss), float(run)])))
         p = self.path(run, step)

@@ -1,7 +1,8 @@
 // Peer-memory communication kernels (NVLink / NVSwitch, plain loads and stores on peer-mapped
 // addresses; no TMA multicast, no multimem): cross-rank barrier on flag pads, K/V block gather for
-// the ring, Ulysses sequence<->head exchanges, and the two-shot gradient all-reduce with the bf16
-// cast/scale folded in.
+// the ring, Ulysses sequence<->head exchanges, the two-shot gradient all-reduce with the bf16
+// cast/scale folded in, and the transport of the sharded optimiser (fp32 reduce-scatter of the gradients
+// straight from the peers' gradient buffers, all-gather of the updated parameters).
 //
 // Every rank owns an arena of identical layout (csrc/runtime/symm.cpp); `peers[r]` is the address of
 // rank r's arena in this process.  Flags are int32 epochs that only grow, so they are never reset.
@@ -156,8 +157,8 @@ __global__ void a2a_push_rows_f32_kernel(const float* __restrict__ src, int B, i
 
 // ---------------------------------------------------------------------------- gradient all-reduce (two-shot)
 // Phase 1 (after a barrier): rank r owns slice r of the bucket; it reads slice r of every rank's bf16 staging
-// copy (grad * scale, written by cast_f32_bf16), sums in fp32 and writes the result as fp32 into its own
-// gradient buffer and as bf16 back into its own staging slice.
+// copy (grad * scale, written by cast_f32_bf16), sums in fp32, rounds to bf16 (the wire format of this
+// replicated-optimiser path) and writes the rounded result into its own gradient buffer and staging slice.
 // Phase 2 (after another barrier): every rank pulls the reduced bf16 slices of the other ranks into its fp32
 // gradient buffer.
 __global__ void allreduce_reduce_kernel(const uint64_t* __restrict__ peers, long stage_off, float* __restrict__ grad,
@@ -174,10 +175,13 @@ __global__ void allreduce_reduce_kernel(const uint64_t* __restrict__ peers, long
       acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
     }
     const long e = lo + i * 8;
+    // the owner keeps the SAME bf16-rounded values the other ranks will gather, so that the replicated optimiser
+    // states stay bit-identical on every rank
+    const uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+    const float rr[8] = {bf16_lo(o.x), bf16_hi(o.x), bf16_lo(o.y), bf16_hi(o.y), bf16_lo(o.z), bf16_hi(o.z), bf16_lo(o.w), bf16_hi(o.w)};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) if (e + j < n) grad[e + j] = acc[j];
-    *((uint4*)(peers[my_rank] + stage_off) + (lo >> 3) + i) =
-        make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+    for (int j = 0; j < 8; ++j) if (e + j < n) grad[e + j] = rr[j];
+    *((uint4*)(peers[my_rank] + stage_off) + (lo >> 3) + i) = o;
   }
 }
 __global__ void allreduce_gather_kernel(const uint64_t* __restrict__ peers, long stage_off, float* __restrict__ grad,
@@ -192,6 +196,99 @@ __global__ void allreduce_gather_kernel(const uint64_t* __restrict__ peers, long
     const float f[8] = {bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y), bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w)};
 #pragma unroll
     for (int j = 0; j < 8; ++j) if (e + j < n) grad[e + j] = f[j];
+  }
+}
+
+// ---------------------------------------------------------------------------- sharded optimiser transport
+// The flat fp32 gradient buffer of every rank lives at the same arena offset.  It is cut into buckets; inside a
+// bucket of n elements starting at flat index `start`, rank r owns the sub-slice [start + r*per, start + (r+1)*per)
+// (clipped to the bucket), per a multiple of 8.  Reduce-scatter: the owner reads its sub-slice of EVERY rank's
+// gradient buffer in fp32 straight over NVLink (no staging copy, no cast), adds the values in rank order 0..N-1
+// (one fixed order per element: bit-reproducible run to run and identical to what any other rank would compute),
+// scales by 1/N and writes them to its shard-contiguous reduced-gradient buffer.  The loads of up to eight peers
+// are issued before the first add so all links are busy at once.
+__global__ void reduce_scatter_f32_kernel(const uint64_t* __restrict__ peers, long grad_off, long start, long n, long per,
+                                          float* __restrict__ out, int world, int my_rank, float scale) {
+  const long lo = per * my_rank, hi = min(n, lo + per);
+  const long nvec = hi > lo ? (hi - lo) >> 2 : 0;               // every boundary is a multiple of 8 elements
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r0 = 0; r0 < world; r0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (r0 + j < world) v[j] = *((const float4*)(peers[r0 + j] + grad_off) + ((start + lo) >> 2) + i);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (r0 + j < world) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    ((float4*)out)[i] = acc;
+  }
+}
+
+// All-gather by pulling: a buffer (bf16 compute copy of the matrices, or the fp32 copy of the vectors) that lives at
+// the same arena offset on every rank is made whole on this rank by copying, for every bucket segment, the
+// sub-slices the other ranks own from their arenas.  One segment per blockIdx.y.
+struct GatherSeg {
+  long elem_start;      // flat index of the segment's first element
+  long elem_n;          // elements in the segment
+  long bucket_start;    // flat index of the bucket's first element (ownership is counted from here)
+  long per;             // elements per owner inside the bucket
+};
+__global__ void allgather_pull_kernel(const uint64_t* __restrict__ peers, long buf_off, long buf_elem0, int elem_bytes,
+                                      const GatherSeg* __restrict__ segs, int world, int my_rank) {
+  const GatherSeg sg = segs[blockIdx.y];
+  const int epv = 16 / elem_bytes;                          // elements per 16-byte vector
+  const long nvec = sg.elem_n / epv;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    const long e = sg.elem_start + i * epv;
+    const int owner = (int)((e - sg.bucket_start) / sg.per);
+    if (owner == my_rank || owner >= world) continue;
+    const long v = ((e - buf_elem0) * elem_bytes) >> 4;
+    *((uint4*)(peers[my_rank] + buf_off) + v) = *((const uint4*)(peers[owner] + buf_off) + v);
+  }
+}
+
+// Cross-rank sum of one fp32 scalar per rank (the partial squared gradient norms): share_scalar stores this rank's
+// value into slot [my_rank] of every rank's slot row; after a barrier sum_slots adds the N slots in rank order, so
+// every rank obtains the same bits.
+__global__ void share_scalar_kernel(const uint64_t* __restrict__ peers, long slot_off, const float* __restrict__ value,
+                                    int world, int my_rank) {
+  const int r = threadIdx.x;
+  if (r < world) ((float*)(peers[r] + slot_off))[my_rank] = value[0];
+}
+__global__ void sum_slots_kernel(const float* __restrict__ slots, int world, float* __restrict__ out) {
+  float s = 0.f;
+  for (int r = 0; r < world; ++r) s += slots[r];
+  out[0] = s;
+}
+
+// Deterministic dK/dV reduction of the fused ring ("pull" mode): every rank has written its contributions for the
+// whole sequence into a local fp32 buffer at the same arena offset; the owner of a chunk adds the chunk's rows of
+// the contributing ranks in rank order and writes bf16.  One segment per blockIdx.y.
+struct PullSeg {
+  long src_elem;        // first element of the chunk rows inside every rank's full-length buffer
+  long dst_elem;        // first element inside the local output
+  long n;               // elements (multiple of 8)
+  unsigned int mask;    // bit s set: rank s contributes
+  int pad;
+};
+__global__ void dkv_pull_reduce_kernel(const uint64_t* __restrict__ peers, long buf_off, const PullSeg* __restrict__ segs,
+                                       __nv_bfloat16* __restrict__ out, int world) {
+  const PullSeg sg = segs[blockIdx.y];
+  const long nvec = sg.n >> 3;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      if (!((sg.mask >> r) & 1u)) continue;
+      const float4* src = (const float4*)(peers[r] + buf_off) + ((sg.src_elem >> 2) + i * 2);
+      const float4 a = src[0], b = src[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    *((uint4*)(out + sg.dst_elem) + i) =
+        make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
   }
 }
 
@@ -271,4 +368,45 @@ extern "C" int cpb_allreduce_gather(const uint64_t* peers, long stage_off, float
   if (n <= 0) return CPB_OK;
   allreduce_gather_kernel<<<n_ctas, 512, 0, stream>>>(peers, stage_off, grad, n, world, my_rank);
   return check_launch("allreduce_gather");
+}
+
+extern "C" int cpb_reduce_scatter_f32(const uint64_t* peers, long grad_off, long start, long n, long per, float* out,
+                                      int world, int my_rank, float scale, int n_ctas, cudaStream_t stream) {
+  if (n <= 0) return CPB_OK;
+  if ((start % 8) || (per % 8) || (n % 8) || per <= 0)
+    return set_error(CPB_ERR_ARG, "reduce_scatter_f32: start, n and per must be multiples of 8 elements");
+  reduce_scatter_f32_kernel<<<n_ctas < 1 ? 1 : n_ctas, 512, 0, stream>>>(peers, grad_off, start, n, per, out, world, my_rank, scale);
+  return check_launch("reduce_scatter_f32");
+}
+
+// segs: device array of {elem_start, elem_n, bucket_start, per} (four longs each).
+extern "C" int cpb_allgather_pull(const uint64_t* peers, long buf_off, long buf_elem0, int elem_bytes, const void* segs,
+                                  int n_segs, int world, int my_rank, int ctas_per_seg, cudaStream_t stream) {
+  if (n_segs <= 0) return CPB_OK;
+  if (elem_bytes != 2 && elem_bytes != 4) return set_error(CPB_ERR_ARG, "allgather_pull: element size must be 2 or 4");
+  if (n_segs > 65535) return set_error(CPB_ERR_LIMIT, "allgather_pull: at most 65535 segments");
+  dim3 grid(ctas_per_seg < 1 ? 1 : ctas_per_seg, n_segs);
+  allgather_pull_kernel<<<grid, 512, 0, stream>>>(peers, buf_off, buf_elem0, elem_bytes, (const GatherSeg*)segs, world, my_rank);
+  return check_launch("allgather_pull");
+}
+
+extern "C" int cpb_share_scalar(const uint64_t* peers, long slot_off, const float* value, int world, int my_rank,
+                                cudaStream_t stream) {
+  if (world > 32) return set_error(CPB_ERR_LIMIT, "share_scalar: at most 32 ranks");
+  share_scalar_kernel<<<1, 32, 0, stream>>>(peers, slot_off, value, world, my_rank);
+  return check_launch("share_scalar");
+}
+extern "C" int cpb_sum_slots(const float* slots, int world, float* out, cudaStream_t stream) {
+  sum_slots_kernel<<<1, 1, 0, stream>>>(slots, world, out);
+  return check_launch("sum_slots");
+}
+
+// segs: device array of {src_elem, dst_elem, n, mask, pad} (three longs and two ints each).
+extern "C" int cpb_dkv_pull_reduce(const uint64_t* peers, long buf_off, const void* segs, int n_segs, void* out, int world,
+                                   int ctas_per_seg, cudaStream_t stream) {
+  if (n_segs <= 0) return CPB_OK;
+  if (world > 32) return set_error(CPB_ERR_LIMIT, "dkv_pull_reduce: at most 32 ranks");
+  dim3 grid(ctas_per_seg < 1 ? 1 : ctas_per_seg, n_segs);
+  dkv_pull_reduce_kernel<<<grid, 256, 0, stream>>>(peers, buf_off, (const PullSeg*)segs, (__nv_bfloat16*)out, world);
+  return check_launch("dkv_pull_reduce");
 }

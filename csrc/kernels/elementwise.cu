@@ -670,6 +670,43 @@ __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
   }
 }
 
+// AdamW over this rank's shard of a sharded optimiser state.  master/m/v/g are shard-contiguous; every segment
+// (blockIdx.y) maps a run of shard elements to the flat parameter index it updates, so the refreshed compute copy is
+// written at its flat position: bf16 for matrices (decay != 0, flat index < n_decay) and fp32 for vectors.
+struct AdamSeg {
+  long shard_begin;     // first element inside the shard buffers
+  long flat_begin;      // flat parameter index of that element
+  long n;
+  long decay;           // 1: weight decay applies and the compute copy is bf16; 0: no decay, fp32 copy
+};
+__global__ void adamw_sharded_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                                     float* __restrict__ v, __nv_bfloat16* __restrict__ p16, float* __restrict__ p32,
+                                     long n_decay, const AdamSeg* __restrict__ segs, float lr, float b1, float b2,
+                                     float eps, float wd, float bc1, float bc2, float grad_prescale, float clip,
+                                     const float* __restrict__ sumsq, int* __restrict__ flag) {
+  float gs = grad_prescale;
+  if (sumsq) {
+    const float ssq = sumsq[0];
+    if (!isfinite(ssq)) { if (flag && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) flag[0] = 1; return; }
+    const float norm = sqrtf(ssq) * grad_prescale;
+    if (clip > 0.f) gs *= fminf(1.f, clip / (norm + 1e-6f));
+  }
+  const AdamSeg sg = segs[blockIdx.y];
+  const float decay = sg.decay ? (1.f - lr * wd) : 1.f;
+  const float inv_bc2_sqrt = rsqrtf(bc2);
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < sg.n; i += (long)gridDim.x * blockDim.x) {
+    const long s = sg.shard_begin + i, f = sg.flat_begin + i;
+    const float gi = g[s] * gs;
+    float pi = p[s] * decay;
+    const float mi = b1 * m[s] + (1.f - b1) * gi;
+    const float vi = b2 * v[s] + (1.f - b2) * gi * gi;
+    pi -= (lr / bc1) * mi / (sqrtf(vi) * inv_bc2_sqrt + eps);
+    p[s] = pi; m[s] = mi; v[s] = vi;
+    if (sg.decay) p16[f] = __float2bfloat16(pi);
+    else p32[f - n_decay] = pi;
+  }
+}
+
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t n, float scale) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     out[i] = __float2bfloat16(in[i] * scale);
@@ -850,6 +887,20 @@ extern "C" int cpb_sumsq(const float* g, long n, float* partial, unsigned int* t
   sumsq_kernel<<<grid, 256, 0, stream>>>(g, (size_t)n, partial, ticket, out);
   return check_launch("sumsq");
 }
+// segs: device array of {shard_begin, flat_begin, n, decay} (four longs each).
+extern "C" int cpb_adamw_sharded(float* p, const float* g, float* m, float* v, void* p16, float* p32, long n_decay,
+                                 const void* segs, int n_segs, int ctas_per_seg, float lr, float b1, float b2, float eps,
+                                 float wd, int step, float grad_prescale, float clip, const float* sumsq, int* flag,
+                                 cudaStream_t stream) {
+  if (n_segs <= 0) return CPB_OK;
+  if (n_segs > 65535) return set_error(CPB_ERR_LIMIT, "adamw_sharded: at most 65535 segments");
+  const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  dim3 grid(ctas_per_seg < 1 ? 1 : ctas_per_seg, n_segs);
+  adamw_sharded_kernel<<<grid, 256, 0, stream>>>(p, g, m, v, (__nv_bfloat16*)p16, p32, n_decay, (const AdamSeg*)segs, lr, b1, b2,
+                                                 eps, wd, bc1, bc2, grad_prescale, clip, sumsq, flag);
+  return check_launch("adamw_sharded");
+}
+
 extern "C" int cpb_adamw(float* p, const float* g, float* m, float* v, void* p16, long n, float lr, float b1, float b2,
                          float eps, float wd, int step, float grad_prescale, float clip, const float* sumsq, int* flag,
                          cudaStream_t stream) {

@@ -66,7 +66,7 @@ def main():
         if not rel < a.tol:
             ok = False
     eng.check_kernels()
-    wa, wb = eng.flat.master, ref.flat.master
+    wa, wb = eng.flat.full_master(), ref.flat.full_master()
     cos = float((wa.double() @ wb.double()) / (wa.double().norm() * wb.double().norm()))
     dmax = float((wa - wb).abs().max())
     if cos < (0.99999 if a.tol < 1e-3 else 0.999):
