@@ -12,7 +12,11 @@ Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, barrier + 
 sides, max over ranks) over exactly ``--steps`` full optimiser steps with the batch already on the
 device; ``e2e`` repeats the measurement through the same public ``TrainEngine.train_step`` call with the
 per-step host→device copy of the tokens from pinned memory and a device→host read of the loss inside
-the timed region.  ``--impl reference`` reports why the reference cannot run here.
+the timed region.  With more than one GPU two more fields follow, both measured outside the headline's
+timed region: ``ring`` (the same model and sequence under ring attention, the other mode the metric names,
+timed the same way) and ``cp_parity`` (one step of a small model under the same parallelism against an
+unsharded run of the same batch in the same process: relative loss difference and cosine of the averaged
+gradient).  ``--impl reference`` reports why the reference cannot run here.
 """
 from __future__ import annotations
 
@@ -25,8 +29,10 @@ import sys
 import threading
 import time
 
-REF_UNAVAILABLE = ("reference is not installable: its source tree has no setup.py/pyproject.toml and its Makefile needs the "
-                   "absent BluTrain tensor library, MPI and mpic++")
+REF_UNAVAILABLE = ("reference is not installable: its source tree has no setup.py/pyproject.toml, its Makefile needs the "
+                   "absent BluTrain tensor library, MPI and mpic++, and its one Python trainer "
+                   "(Scripts/Pytorch/gpt2_cp_attnstyle_fp32.py) imports three private torch.distributed ring-attention "
+                   "symbols that torch 2.11 no longer has")
 
 MODELS = {
     # BASELINE config 3 / 5: Llama-style 1B
@@ -108,6 +114,7 @@ def main() -> None:
     ap.add_argument("--yarn-scale", type=float, default=1.0, help="YaRN position-scaling factor (1 = plain RoPE)")
     ap.add_argument("--recompute", default="selective")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the ring timing and the cp_parity step (N > 1)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -133,79 +140,128 @@ def main() -> None:
 
     m = dict(MODELS[args.model])
     family = m.pop("family")
-    mode = args.mode
     cp = args.cp or world
     dp = world // cp
-    usize = args.ulysses_size or (2 if (mode == "hybrid" and cp % 2 == 0) else 1)
     env = {"CP_SIZE": str(cp)}
     if args.yarn_scale != 1.0:
         env.update(YARN_SCALE=str(args.yarn_scale), YARN_ORIG_MAXPOS=str(args.T / args.yarn_scale))
-    cfg = Config.from_env(family, world, env=env).replace(
-        **m, T=args.T, B=args.batch, cp_size=cp, attn_mode=mode, rotator=args.rotator, ulysses_size=usize,
-        dtype="bf16", recompute=args.recompute, max_steps=1000, warmup_steps=10, global_batch=args.batch * args.T * dp,
-        checkpointing=False)
-    eng = TrainEngine(cfg, dev)
+    tokens_per_step = args.batch * args.T * dp
 
-    gen = torch.Generator().manual_seed(1234 + eng.cp.dp_rank)   # all CP ranks of a replica read the same batch; replicas differ
-    n_batches = 4
-    host = [torch.randint(0, cfg.vocab_size, (args.batch, args.T + 1), generator=gen).pin_memory() for _ in range(n_batches)]
-    devb = [h.to(dev) for h in host]
-
-    def step_dev(i):
-        b = devb[i % n_batches]
-        return eng.train_step(b[:, :-1], b[:, 1:])
-
-    def step_e2e(i):
-        h = host[i % n_batches]
-        loss = eng.train_step(h[:, :-1], h[:, 1:])      # H2D of the pinned tokens happens inside
-        return float(loss)                               # D2H read of the step's loss
+    def make_cfg(mode, **over):
+        usize = args.ulysses_size or (2 if (mode == "hybrid" and cp % 2 == 0) else 1)
+        kw = dict(m, T=args.T, B=args.batch, cp_size=cp, attn_mode=mode, rotator=args.rotator, ulysses_size=usize,
+                  dtype="bf16", recompute=args.recompute, max_steps=1000, warmup_steps=10,
+                  global_batch=args.batch * args.T * dp, checkpointing=False)
+        kw.update(over)
+        return Config.from_env(family, world, env=env).replace(**kw), usize
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step_dev(i)
-    eng.check_kernels()
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
-    sampler = ClockSampler(local)
-    barrier()
-    sampler.start()
-    launches0 = nv.LAUNCHES[0]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(args.steps):
-        loss = step_dev(args.warmup + i)
-    e1.record()
-    barrier()
-    launches = nv.LAUNCHES[0] - launches0
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.stop()
-    eng.check_kernels()
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    tokens_per_step = args.batch * args.T * dp
-    value = tokens_per_step * args.steps / (ms / 1e3)
-    final_loss = float(eng.global_loss(loss))
+    def measure(mode, with_e2e, sample_clocks):
+        """Build the engine for ``mode``, warm up, time ``--steps`` optimiser steps on the device (and end to end)."""
+        cfg, usize = make_cfg(mode)
+        eng = TrainEngine(cfg, dev)
+        gen = torch.Generator().manual_seed(1234 + eng.cp.dp_rank)   # all CP ranks of a replica read the same batch; replicas differ
+        n_batches = 4
+        host = [torch.randint(0, cfg.vocab_size, (args.batch, args.T + 1), generator=gen).pin_memory() for _ in range(n_batches)]
+        devb = [h.to(dev) for h in host]
 
-    e2e = None
-    if not args.no_e2e:
-        step_e2e(0)
+        def step_dev(i):
+            b = devb[i % n_batches]
+            return eng.train_step(b[:, :-1], b[:, 1:])
+
+        def step_e2e(i):
+            h = host[i % n_batches]
+            loss = eng.train_step(h[:, :-1], h[:, 1:])      # H2D of the pinned tokens happens inside
+            return float(loss)                               # D2H read of the step's loss
+
+        for i in range(args.warmup):
+            step_dev(i)
+        eng.check_kernels()
+        sampler = ClockSampler(local) if sample_clocks else None
+        barrier()
+        if sampler:
+            sampler.start()
+        launches0 = nv.LAUNCHES[0]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
         for i in range(args.steps):
-            step_e2e(i + 1)
+            loss = step_dev(args.warmup + i)
         e1.record()
         barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e = {"value": tokens_per_step * args.steps / (float(t.item()) / 1e3), "unit": "tokens/s",
-               "h2d_bytes_per_step": int(2 * args.batch * args.T * 8), "d2h_bytes_per_step": 4}
+        launches = nv.LAUNCHES[0] - launches0
+        ms = max_over_ranks(e0.elapsed_time(e1))
+        clocks = sampler.stop() if sampler else None
+        eng.check_kernels()
+        res = {"cfg": cfg, "usize": usize, "ms": ms, "value": tokens_per_step * args.steps / (ms / 1e3), "clocks": clocks,
+               "launches": int(launches), "final_loss": float(eng.global_loss(loss)), "e2e": None,
+               "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30, "sharded_optimizer": bool(eng.flat.sharded)}
+        if with_e2e:
+            step_e2e(0)
+            barrier()
+            e0.record()
+            for i in range(args.steps):
+                step_e2e(i + 1)
+            e1.record()
+            barrier()
+            ms2 = max_over_ranks(e0.elapsed_time(e1))
+            res["e2e"] = {"value": tokens_per_step * args.steps / (ms2 / 1e3), "unit": "tokens/s",
+                          "h2d_bytes_per_step": int(2 * args.batch * args.T * 8), "d2h_bytes_per_step": 4}
+        eng.check_kernels()
+        eng.close()
+        del eng, devb, host
+        torch.cuda.empty_cache()
+        return res
+
+    def cp_parity(mode):
+        """One optimiser-free step of a small model under the job's parallelism against an unsharded run of the same
+        global batch on this GPU: relative loss difference and cosine of the averaged gradient (max / min over ranks)."""
+        small = dict(MODELS["tiny"])
+        small.pop("family")
+        Tp = 2048 * cp
+        usize = args.ulysses_size or (2 if (mode == "hybrid" and cp % 2 == 0) else 1)
+        pcfg = Config.from_env("llama", world, env={"CP_SIZE": str(cp)}).replace(
+            **small, T=Tp, B=1, cp_size=cp, attn_mode=mode, rotator=args.rotator, ulysses_size=usize, dtype="bf16",
+            recompute="none", max_steps=10, warmup_steps=1, global_batch=Tp * dp, checkpointing=False)
+        e = TrainEngine(pcfg, dev)
+        r = TrainEngine(pcfg.replace(world_size=1, cp_size=1, ulysses_size=1, attn_mode="ring"), dev, standalone=True)
+        g = torch.Generator().manual_seed(4321)
+        tok = torch.randint(0, pcfg.vocab_size, (dp, Tp + 1), generator=g).to(dev)
+        mine = tok[e.cp.dp_rank:e.cp.dp_rank + 1]
+        l_cp = float(e.global_loss(e.forward_backward(mine[:, :-1], mine[:, 1:], 1, True)))
+        l_ref = 0.0
+        for d in range(dp):
+            l_ref += float(r.forward_backward(tok[d:d + 1, :-1], tok[d:d + 1, 1:], accum=dp, last=True)) / dp
+        ga, gb = e.flat.full_reduced_grad().double(), r.flat.grad.double()
+        cos = float((ga @ gb) / (ga.norm() * gb.norm() + 1e-30))
+        t = torch.tensor([abs(l_cp - l_ref) / abs(l_ref), -cos], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e.check_kernels()
+        e.close()
+        return {"loss_rel": float(t[0]), "grad_cos": float(-t[1]), "model": "tiny", "seq_len": Tp, "mode": mode}
+
+    mode = args.mode
+    main_res = measure(mode, not args.no_e2e, True)
+    cfg, usize, ms = main_res["cfg"], main_res["usize"], main_res["ms"]
+    value, clocks, e2e, launches, final_loss = (main_res[k] for k in ("value", "clocks", "e2e", "launches", "final_loss"))
+    ring_res = parity = None
+    if world > 1 and not args.no_extras:
+        parity = {mode: cp_parity(mode)}
+        if mode != "ring" and cp > 1:
+            rr = measure("ring", False, False)
+            ring_res = {"value": rr["value"], "unit": "tokens/s", "ms_per_step": rr["ms"] / args.steps, "steps": args.steps,
+                        "warmup": args.warmup, "final_loss": rr["final_loss"], "parallelism": f"ring{cp}" + (f"xdp{dp}" if dp > 1 else "")}
+            parity["ring"] = cp_parity("ring")
 
     # model FLOPs per step (whole job): dense matmuls 6*P_active*tokens + causal attention 3.5 * 2*T^2*d_attn*L
     p_dense = cfg.n_layer * (cfg.n_embd * (cfg.n_head + 2 * cfg.n_kv_head) * cfg.head_dim + cfg.n_head * cfg.head_dim * cfg.n_embd
@@ -229,9 +285,9 @@ def main() -> None:
             "attn_share_of_flops": attn_flops / flops,
             "final_loss": final_loss,
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
-            "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30,
+            "peak_mem_gb": main_res["peak_mem_gb"], "sharded_optimizer": main_res["sharded_optimizer"],
+            "ring": ring_res, "cp_parity": parity,
         }))
-    eng.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

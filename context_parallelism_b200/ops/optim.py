@@ -84,9 +84,10 @@ class ShardPlan:
 
 class FlatParams:
     def __init__(self, named_params: Iterable[Tuple[str, torch.nn.Parameter]], bf16_matrices: bool,
-                 bucket_mb: int = 25, shard=None):
+                 bucket_mb: int = 25, shard=None, bucket_elems: Optional[int] = None):
         """``shard``: the peer-memory transport (``parallel.fused.FusedComm``) when the optimiser state is to be
-        sharded over its world group; ``None`` keeps everything replicated."""
+        sharded over its world group; ``None`` keeps everything replicated.  ``bucket_elems`` overrides the bucket size
+        given in MB (tests use tiny buckets)."""
         seen, decay, nodecay = set(), [], []
         for name, p in named_params:
             if id(p) in seen or not p.requires_grad:
@@ -104,7 +105,7 @@ class FlatParams:
         dev = (decay + nodecay)[0][1].device
         self.device = dev
         self.bf16 = bool(bf16_matrices and dev.type == "cuda")
-        self.buckets = plan_buckets(self.entries, self.total, max(1, bucket_mb) * (1 << 20) // 4)
+        self.buckets = plan_buckets(self.entries, self.total, bucket_elems or max(1, bucket_mb) * (1 << 20) // 4)
         self.shard = shard if (shard is not None and dev.type == "cuda" and self.bf16) else None
         self.plan: Optional[ShardPlan] = None
         self._by_name = {name: (p, o, n) for name, p, o, n in self.entries}
@@ -275,18 +276,22 @@ class FlatParams:
             self.m[o:o + n].copy_(mm)
             self.v[o:o + n].copy_(vv)
 
-    def grad_norm(self, prescale: float = 1.0) -> torch.Tensor:
-        """Global L2 norm of the (reduced) gradient times ``prescale`` as a device scalar (no host sync)."""
+    def local_sumsq_(self) -> None:
+        """Sum of squares of what this rank holds of the (reduced) gradient into ``self.sumsq`` (device, no sync)."""
         if self.sharded:
-            fc = self.shard
             nv.call("sumsq", nv.ptr(self.gshard), nv.l(self.plan.shard_total), nv.ptr(self._scratch), nv.ptr(self._ticket),
                     nv.ptr(self.sumsq), nv.stream_ptr(self.device))
-            fc.sum_over_ranks_(self.sumsq, self.slots_off, self.slots)
         elif self.device.type == "cuda":
             nv.call("sumsq", nv.ptr(self.grad), nv.l(self.total), nv.ptr(self._scratch), nv.ptr(self._ticket),
                     nv.ptr(self.sumsq), nv.stream_ptr(self.device))
         else:
             self.sumsq[0] = (self.grad.double() ** 2).sum().float()
+
+    def grad_norm(self, prescale: float = 1.0) -> torch.Tensor:
+        """Global L2 norm of the (reduced) gradient times ``prescale`` as a device scalar (no host sync)."""
+        self.local_sumsq_()
+        if self.sharded:
+            self.shard.sum_over_ranks_(self.sumsq, self.slots_off, self.slots)
         return self.sumsq.sqrt() * prescale
 
 
@@ -308,13 +313,8 @@ class AdamW:
         norm = f.grad_norm(grad_prescale)
         b1, b2 = self.betas
         if f.sharded:
-            fc = f.shard
-            if f._adam_segs is not None:
-                nv.call("adamw_sharded", nv.ptr(f.master), nv.ptr(f.gshard), nv.ptr(f.m), nv.ptr(f.v), nv.ptr(f.p16), nv.ptr(f.p32),
-                        nv.l(f.n_decay), nv.ptr(f._adam_segs), nv.i(f._adam_segs.shape[0]), nv.i(16), nv.f(lr), nv.f(b1), nv.f(b2),
-                        nv.f(self.eps), nv.f(self.wd), nv.i(self.step_count), nv.f(grad_prescale), nv.f(clip), nv.ptr(f.sumsq),
-                        nv.ptr(f.skip_flag), nv.stream_ptr(f.device))
-            fc.allgather_params(f)
+            self.update_shard_(lr, clip, grad_prescale)
+            f.shard.allgather_params(f)
         elif f.device.type == "cuda":
             for lo, hi, wd in ((0, f.n_decay, self.wd), (f.n_decay, f.total, 0.0)):
                 if hi <= lo:
@@ -335,6 +335,17 @@ class AdamW:
                 if hi > lo:
                     ref.adamw_step(f.master[lo:hi], g[lo:hi], f.m[lo:hi], f.v[lo:hi], self.step_count, lr, b1, b2, self.eps, wd)
         return norm
+
+    def update_shard_(self, lr: float, clip: float, grad_prescale: float = 1.0) -> None:
+        """Sharded layout: AdamW on the owned slices, from ``flat.gshard`` and the global squared norm in
+        ``flat.sumsq``; writes the refreshed compute copies at their flat positions (one launch)."""
+        f = self.flat
+        b1, b2 = self.betas
+        if f._adam_segs is not None:
+            nv.call("adamw_sharded", nv.ptr(f.master), nv.ptr(f.gshard), nv.ptr(f.m), nv.ptr(f.v), nv.ptr(f.p16), nv.ptr(f.p32),
+                    nv.l(f.n_decay), nv.ptr(f._adam_segs), nv.i(f._adam_segs.shape[0]), nv.i(16), nv.f(lr), nv.f(b1), nv.f(b2),
+                    nv.f(self.eps), nv.f(self.wd), nv.i(self.step_count), nv.f(grad_prescale), nv.f(clip), nv.ptr(f.sumsq),
+                    nv.ptr(f.skip_flag), nv.stream_ptr(f.device))
 
     def state_dict(self) -> Dict[str, torch.Tensor]:
         """Adam moments by parameter name (collective when the state is sharded: call it on every rank)."""

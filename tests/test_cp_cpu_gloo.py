@@ -30,6 +30,13 @@ def test_ring_rotators_ws2(rotator):
     run_worker(2, "--mode", "ring", "--rotator", rotator, "--tol", 1e-4)
 
 
+@pytest.mark.parametrize("extra", [["--lb", 0], ["--recompute", "full"], ["--recompute-k", 1]])
+def test_ring_ws2_variants(extra):
+    """Contiguous (not load-balanced) shards, full activation recompute (the ring re-runs inside backward), and
+    K/V re-rotation in backward instead of saved blocks (``CP_RECOMPUTE_K``)."""
+    run_worker(2, "--mode", "ring", "--rotator", "p2p", "--tol", 1e-4, *extra)
+
+
 def test_ring_ws4_gpt2():
     run_worker(4, "--mode", "ring", "--rotator", "p2p", "--family", "gpt2", "--tol", 1e-4)
 
