@@ -115,6 +115,8 @@ def main() -> None:
     ap.add_argument("--recompute", default="selective")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the ring timing and the cp_parity step (N > 1)")
+    ap.add_argument("--phases", action="store_true", help="after the timed steps run one more step with every kernel launch "
+                                                          "bracketed by CUDA events and report device ms per kernel name")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -217,6 +219,22 @@ def main() -> None:
             ms2 = max_over_ranks(e0.elapsed_time(e1))
             res["e2e"] = {"value": tokens_per_step * args.steps / (ms2 / 1e3), "unit": "tokens/s",
                           "h2d_bytes_per_step": int(2 * args.batch * args.T * 8), "d2h_bytes_per_step": 4}
+        if args.phases:
+            # one more step, outside every timed region, with per-launch CUDA events (max over ranks per kernel name)
+            barrier()
+            nv.profile_start()
+            e0.record()
+            step_dev(0)
+            e1.record()
+            prof = nv.profile_stop()
+            names = sorted(prof)
+            t = torch.tensor([prof[k][1] for k in names] + [e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+            if world > 1:
+                lists = [None] * world
+                dist.all_gather_object(lists, names)
+                assert all(l == names for l in lists), "ranks launched different kernels"
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res["phases"] = {"step_ms": float(t[-1]), "kernels": {k: {"calls": prof[k][0], "ms": round(float(t[i]), 3)} for i, k in enumerate(names)}}
         eng.check_kernels()
         eng.close()
         del eng, devb, host
@@ -286,7 +304,7 @@ def main() -> None:
             "final_loss": final_loss,
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
             "peak_mem_gb": main_res["peak_mem_gb"], "sharded_optimizer": main_res["sharded_optimizer"],
-            "ring": ring_res, "cp_parity": parity,
+            "ring": ring_res, "cp_parity": parity, "phases": main_res.get("phases"),
         }))
     if world > 1:
         dist.barrier()

@@ -64,6 +64,7 @@ def ptr(t: Optional[torch.Tensor]) -> c_void_p:
 
 LAUNCHES = [0]          # number of kernel launchers invoked (each launches exactly one of our kernels)
 _FN_CACHE = {}
+_PROFILE = None         # name -> list of (start event, end event) while a per-kernel device timing is being taken
 
 
 def call(name: str, *args) -> None:
@@ -74,9 +75,32 @@ def call(name: str, *args) -> None:
         fn.restype = c_int
         _FN_CACHE[name] = fn
     LAUNCHES[0] += 1
-    rc = fn(*args)
+    if _PROFILE is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = fn(*args)
+        e1.record()
+        _PROFILE.setdefault(name, []).append((e0, e1))
+    else:
+        rc = fn(*args)
     if rc != 0:
         check(rc, name)
+
+
+def profile_start() -> None:
+    """Start timing every launcher call with a pair of CUDA events on the stream it is issued to (diagnostics:
+    device time per kernel name without a profiler; for the cross-rank barrier kernels this is the time spent
+    waiting for the slowest peer)."""
+    global _PROFILE
+    _PROFILE = {}
+
+
+def profile_stop():
+    """Stop timing; returns ``{name: (calls, total_ms)}`` after one device synchronisation."""
+    global _PROFILE
+    prof, _PROFILE = _PROFILE, None
+    torch.cuda.synchronize()
+    return {k: (len(v), sum(a.elapsed_time(b) for a, b in v)) for k, v in (prof or {}).items()}
 
 
 # --------------------------------------------------------------------------- kernel status words

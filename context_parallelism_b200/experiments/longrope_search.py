@@ -69,10 +69,9 @@ def key_of(lam: Sequence[float], n_hat: int) -> str:
 
 
 def write_factors(path: str, lam: Sequence[float], n_hat: int, s: float, search_len: int) -> None:
-    tmp = path + ".tmp"
-    with open(tmp, "w") as f:
-        f.write(f"n_hat={n_hat}\ns={int(s)}\nsearch_len={search_len}\n" + " ".join(f"{v:.6f}" for v in lam) + "\n")
-    os.replace(tmp, path)
+    """Candidate file in the layout both trainers read (bluscriptCP.cpp:538-572)."""
+    from ..ops.rope import write_longrope_factors
+    write_longrope_factors(path, lam, n_hat, s, search_len)
 
 
 # ----------------------------------------------------------------------------- evaluator workers
@@ -136,6 +135,7 @@ class Evaluator:
             if k not in self.memo and k not in [t[0] for t in todo]:
                 todo.append((k, c))
         queue = list(enumerate(todo))
+        deaths: Dict[str, int] = {}
 
         def run(worker: Worker) -> None:
             while True:
@@ -150,6 +150,9 @@ class Evaluator:
                     with self._lock:
                         queue.insert(0, (i, (k, c)))
                         self.redispatched += 1
+                        deaths[k] = deaths.get(k, 0) + 1
+                        if deaths[k] > 3:           # the same candidate keeps killing its evaluator: give up, do not spin
+                            return
                     try:
                         worker.start()
                     except Exception:

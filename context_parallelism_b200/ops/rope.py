@@ -64,14 +64,27 @@ def gather_cache_rows(cache: torch.Tensor, labels: torch.Tensor) -> torch.Tensor
     return out
 
 
-def parse_longrope_factors(path: str):
-    """LongRoPE factors file: ``key=value`` header lines (``n_hat``, ``s``, ``search_len``) and one line of
-    whitespace/comma separated λ values (``lambda=...`` or bare).  Returns ``(lam, n_hat, s, search_len)``."""
-    lam, n_hat, s, slen = None, 0, 0, 0
+def parse_longrope_factors(path: str, half: int = 0):
+    """LongRoPE factors file in the reference's layout (Scripts/Blutrain/bluscriptCP.cpp:538-572): whitespace
+    separated tokens, keys in any order,
+
+        n_hat <int>
+        s <int>                extension ratio the search used
+        S_search <int>         target length of the search
+        lambda <f0> <f1> ...   head_dim/2 non-decreasing values >= 1
+
+    a token starting with ``#`` comments out the rest of its line.  Also accepted, for files written by earlier
+    versions of this package: ``key=value`` header lines with a bare line of λ values.  ``half`` (head_dim / 2), when
+    given, is the exact number of λ values required.  Returns ``(lam, n_hat, s, search_len)``; raises ``ValueError``
+    on any malformation (missing ``n_hat``, too few values, a value below 1, a decreasing value)."""
     with open(path) as f:
-        for line in f:
+        text = f.read()
+    lam, n_hat, s, slen = None, -1, -1, -1
+    lines = [ln.split("#", 1)[0] for ln in text.splitlines()]
+    if any("=" in ln for ln in lines):
+        for line in lines:
             line = line.strip()
-            if not line or line.startswith("#"):
+            if not line:
                 continue
             if "=" in line:
                 k, v = line.split("=", 1)
@@ -84,8 +97,60 @@ def parse_longrope_factors(path: str):
                     slen = int(float(v))
                 elif k in ("lambda", "factors"):
                     lam = [float(t) for t in v.replace(",", " ").split()]
+                else:
+                    raise ValueError(f"{path}: unexpected key {k!r}")
             else:
                 lam = [float(t) for t in line.replace(",", " ").split()]
-    if lam is None:
-        raise ValueError(f"{path}: no lambda vector found")
-    return lam, n_hat, s, slen
+    else:
+        toks = " ".join(lines).split()
+        i = 0
+
+        def number(kind, what):
+            nonlocal i
+            i += 1
+            if i >= len(toks):
+                raise ValueError(f"{path}: bad {what}")
+            try:
+                return kind(toks[i])
+            except ValueError:
+                raise ValueError(f"{path}: bad {what}") from None
+        while i < len(toks):
+            t = toks[i]
+            if t == "n_hat":
+                n_hat = number(int, "n_hat")
+            elif t == "s":
+                s = number(int, "s")
+            elif t == "S_search":
+                slen = number(int, "S_search")
+            elif t == "lambda":
+                lam = []
+                while i + 1 < len(toks) and (half <= 0 or len(lam) < half):
+                    try:
+                        lam.append(float(toks[i + 1]))
+                    except ValueError:
+                        break
+                    i += 1
+            else:
+                raise ValueError(f"{path}: unexpected token {t!r}")
+            i += 1
+    if not lam:
+        raise ValueError(f"{path}: missing 'lambda'")
+    if half > 0 and len(lam) != half:
+        raise ValueError(f"{path}: expected {half} lambda values, found {len(lam)}")
+    if n_hat < 0:
+        raise ValueError(f"{path}: missing 'n_hat'")
+    for j, v in enumerate(lam):
+        if not v >= 1.0:
+            raise ValueError(f"{path}: lambda must be >= 1")
+        if j > 0 and v < lam[j - 1]:
+            raise ValueError(f"{path}: lambda must be non-decreasing")
+    return lam, n_hat, max(s, 0), max(slen, 0)
+
+
+def write_longrope_factors(path: str, lam, n_hat: int, s: float, search_len: int) -> None:
+    """Write a factors file the reference's trainer reads (``n_hat`` / ``s`` / ``S_search`` / ``lambda`` tokens), atomically."""
+    import os
+    tmp = path + ".tmp"
+    with open(tmp, "w") as f:
+        f.write(f"n_hat {int(n_hat)}\ns {int(s)}\nS_search {int(search_len)}\nlambda " + " ".join(f"{float(v):.6f}" for v in lam) + "\n")
+    os.replace(tmp, path)

@@ -499,20 +499,24 @@ class _FusedRingFn(torch.autograd.Function):
                 dbg.compare_kv(call, sent, received, owners, fc.ring_pg)
             dbg.dump(dbg.d.dump_cp_out, "cp_out", call, out=out, lse=lse)
             dbg.sync_if(dbg.d.fwd_sync_return)
+        # The slot travels as a (host) saved tensor, not as a ctx attribute: under activation recomputation backward
+        # runs on the ORIGINAL ctx with the saved tensors of the re-run forward, and the re-run published into a new slot.
+        slot_t = torch.tensor([slot], dtype=torch.int64)
         if fc.share_ring_slots:
-            ctx.save_for_backward(q, out, lse, pos32, k, v)
+            ctx.save_for_backward(q, out, lse, pos32, slot_t, k, v)
         else:
-            ctx.save_for_backward(q, out, lse, pos32)
-        ctx.fc, ctx.rb, ctx.slot, ctx.scale = fc, rb, slot, scale
+            ctx.save_for_backward(q, out, lse, pos32, slot_t)
+        ctx.fc, ctx.rb, ctx.scale = fc, rb, scale
         return out
 
     @staticmethod
     def backward(ctx, do):
-        q, out, lse, pos32 = ctx.saved_tensors[:4]
-        fc, rb, slot, scale = ctx.fc, ctx.rb, ctx.slot, ctx.scale
+        q, out, lse, pos32, slot_t = ctx.saved_tensors[:5]
+        fc, rb, scale = ctx.fc, ctx.rb, ctx.scale
+        slot = int(slot_t.item())
         do = do.contiguous()
         if fc.share_ring_slots:
-            rb, slot = ring_fwd_publish(fc, ctx.saved_tensors[4], ctx.saved_tensors[5])
+            rb, slot = ring_fwd_publish(fc, ctx.saved_tensors[5], ctx.saved_tensors[6])
         ring_bwd_prepare(fc, rb)
         fc.barrier(fc.g_ring)                  # every accumulator is zero, every published K/V is still in place
         dq = ring_bwd_compute(fc, rb, slot, q, out, lse, do, pos32, scale)
@@ -675,14 +679,15 @@ class _FusedUlyssesFn(torch.autograd.Function):
                 dbg.selfcheck("fused ulysses forward", call, {"out": out, "lse": lse}, again)
             dbg.dump(dbg.d.dump_cp_out, "cp_out", call, out=out, lse=lse)
             dbg.sync_if(dbg.d.fwd_sync_return)
-        ctx.save_for_backward(lse)
-        ctx.fc, ctx.ub, ctx.slot, ctx.scale = fc, ub, slot, scale
+        ctx.save_for_backward(lse, torch.tensor([slot], dtype=torch.int64))     # slot as a saved tensor: see _FusedRingFn
+        ctx.fc, ctx.ub, ctx.scale = fc, ub, scale
         return out
 
     @staticmethod
     def backward(ctx, do):
-        (lse,) = ctx.saved_tensors
-        fc, ub, slot, scale = ctx.fc, ctx.ub, ctx.slot, ctx.scale
+        lse, slot_t = ctx.saved_tensors
+        fc, ub, scale = ctx.fc, ctx.ub, ctx.scale
+        slot = int(slot_t.item())
         g = fc.g_uly
         uly_bwd_push(fc, ub, slot, do.contiguous())
         fc.barrier(g)

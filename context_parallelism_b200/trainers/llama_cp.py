@@ -42,7 +42,7 @@ def install_context_extension(cfg: Config, eng: TrainEngine):
     factor = int(round(cfg.yarn.scale))
     source = None
     if cfg.longrope_factors:
-        lam, n_hat, s, slen = R.parse_longrope_factors(cfg.longrope_factors)
+        lam, n_hat, s, slen = R.parse_longrope_factors(cfg.longrope_factors, cfg.head_dim // 2)
         mscale = cfg.longrope_mscale
         if cfg.cream_mode != "off":
             if slen and slen != factor * cfg.T:
@@ -131,7 +131,7 @@ def longrope_search_loop(cfg: Config, eng: TrainEngine) -> None:
                 msg[0] = -1
             else:
                 try:
-                    lam, n_hat, s, _ = R.parse_longrope_factors(line.strip())
+                    lam, n_hat, s, _ = R.parse_longrope_factors(line.strip(), cfg.head_dim // 2)
                     from ..ops.reference import validate_longrope
                     validate_longrope(lam, cfg.head_dim, n_hat)
                     msg[0], msg[1], msg[2] = 1, n_hat, s

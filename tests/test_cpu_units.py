@@ -204,3 +204,27 @@ def test_gamma_grad_accumulation_rule():
         parts.append(gg.grad)
     assert torch.allclose(sum(parts) / N, full, atol=1e-6)
     assert not torch.allclose(sum(parts), full, atol=1e-3)
+
+
+def test_longrope_factor_file_reference_layout(tmp_path):
+    """``n_hat <int>`` / ``s <int>`` / ``S_search <int>`` / ``lambda f0 f1 ...`` tokens in any order, ``#`` comments
+    (Scripts/Blutrain/bluscriptCP.cpp:538-572); what the search tool writes is read back unchanged; malformed files
+    are refused with the reference's conditions."""
+    from context_parallelism_b200.ops import rope as R
+    p = tmp_path / "f.txt"
+    p.write_text("# GA best\nlambda 1.0 1.25 2.5 4.0   # tail comment\nS_search 32768 n_hat 4\ns 8\n")
+    assert R.parse_longrope_factors(str(p), 4) == ([1.0, 1.25, 2.5, 4.0], 4, 8, 32768)
+    R.write_longrope_factors(str(p), [1.0, 2.0, 2.0, 3.5], 2, 8, 4096)
+    assert p.read_text().split() == ["n_hat", "2", "s", "8", "S_search", "4096", "lambda", "1.000000", "2.000000", "2.000000", "3.500000"]
+    assert R.parse_longrope_factors(str(p), 4) == ([1.0, 2.0, 2.0, 3.5], 2, 8, 4096)
+    for text in ("lambda 1 2 3 4\n",                      # no n_hat
+                 "n_hat 0\nlambda 1 2 3\n",               # too few values
+                 "n_hat 0\nlambda 0.5 1 2 3\n",           # below 1
+                 "n_hat 0\nlambda 1 3 2 4\n",             # decreasing
+                 "n_hat x\nlambda 1 2 3 4\n",             # bad integer
+                 "n_hat 0\nfoo 3\nlambda 1 2 3 4\n"):     # unknown token
+        p.write_text(text)
+        with pytest.raises(ValueError):
+            R.parse_longrope_factors(str(p), 4)
+    p.write_text("n_hat=1\ns=4\nsearch_len=64\n1.0 2.0 3.0 4.0\n")      # the older key=value form still loads
+    assert R.parse_longrope_factors(str(p), 4) == ([1.0, 2.0, 3.0, 4.0], 1, 4, 64)

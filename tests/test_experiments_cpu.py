@@ -18,7 +18,8 @@ FAKE = textwrap.dedent('''
         line = line.strip()
         if line in ("quit", "exit"):
             break
-        vals = [float(t) for t in open(line).read().split("\\n")[3].split()]
+        toks = open(line).read().split()
+        vals = [float(t) for t in toks[toks.index("lambda") + 1:]]       # the reference's file layout
         if any(b < a for a, b in zip(vals, vals[1:])):
             print("ERR not monotone", flush=True); continue
         n += 1

@@ -68,11 +68,12 @@ def test_eval_ppl_is_cp_invariant(tmp_path):
 
 def test_longrope_resident_evaluator(tmp_path):
     good = tmp_path / "good.txt"
-    good.write_text("n_hat=4\ns=2\nsearch_len=64\n" + " ".join(["1.0", "1.5", "2.0", "2.0"]) + "\n")
+    # the reference's file layout (Scripts/Blutrain/bluscriptCP.cpp:538-572)
+    good.write_text("# searched factors\nn_hat 4\ns 2\nS_search 64\nlambda 1.0 1.5 2.0 2.0\n")
     bad = tmp_path / "bad.txt"
-    bad.write_text("2.0 1.0 1.0 1.0\n")                                   # not monotone -> rejected
+    bad.write_text("n_hat 0\nlambda 2.0 1.0 1.0 1.0\n")                   # not monotone -> rejected
     ident = tmp_path / "ident.txt"
-    ident.write_text("1.0 1.0 1.0 1.0\n")
+    ident.write_text("lambda 1.0 1.0 1.0 1.0\nn_hat 0\n")
     stdin = f"{ident}\n{bad}\n{good}\n{ident}\nquit\n"
     out = run("context_parallelism_b200.trainers.llama_cp", {"CP_CKPT": "0", "CP_LONGROPE_SEARCH": "1", "CP_EVAL_WINDOWS": "1",
                                                              "CP_ATTN_MODE": "ring", "CP_ROTATOR": "p2p"}, nproc=2, stdin=stdin)
