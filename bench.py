@@ -142,6 +142,8 @@ def main() -> None:
 
     m = dict(MODELS[args.model])
     family = m.pop("family")
+    if args.model == "llama8b":
+        os.environ.setdefault("CP_INIT_DEVICE", "1")      # 8 B random-init parameters: draw them on the GPU
     cp = args.cp or world
     dp = world // cp
     env = {"CP_SIZE": str(cp)}

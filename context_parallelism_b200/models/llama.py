@@ -29,7 +29,7 @@ from ..parallel.cp_attention import CPAttention, CPContext
 
 
 def _padded_normal(rows: int, rows_padded: int, cols: int, gen: torch.Generator) -> torch.Tensor:
-    w = torch.zeros(rows_padded, cols)
+    w = torch.zeros(rows_padded, cols, device=gen.device)
     w[:rows].normal_(0.0, 0.02, generator=gen)
     return w
 
@@ -42,7 +42,7 @@ class LlamaBlock(nn.Module):
         resid = 1.0 / math.sqrt(2.0 * cfg.n_layer)
 
         def normal(shape, std):
-            return nn.Parameter(torch.empty(shape).normal_(0.0, std, generator=gen))
+            return nn.Parameter(torch.empty(shape, device=gen.device).normal_(0.0, std, generator=gen))
         self.q_gamma = nn.Parameter(torch.ones(hd))
         self.k_gamma = nn.Parameter(torch.ones(hd))
         self.attn_norm = nn.Parameter(torch.ones(d))
@@ -74,9 +74,13 @@ class Llama(nn.Module):
         super().__init__()
         self.cfg = cfg
         self.cp = cp or CPContext.single(cfg)
-        gen = torch.Generator().manual_seed(cfg.seed if seed is None else seed)
-        # every tensor is drawn from the CPU generator (same values on every rank and on the CPU oracle) and moved to
-        # the device at once, so the host never holds more than one layer of an 8B-parameter model
+        # Every tensor is drawn from the CPU generator (same values on every rank and on the CPU oracle) and moved to
+        # the device at once, so the host never holds more than one layer of an 8B-parameter model.  CP_INIT_DEVICE=1
+        # draws on the device instead (seconds instead of minutes for billions of parameters; the values then differ
+        # from the CPU stream, rank 0's are broadcast to every rank either way).
+        import os
+        on_dev = os.environ.get("CP_INIT_DEVICE", "0") == "1" and torch.device(device).type == "cuda"
+        gen = torch.Generator(device=device if on_dev else "cpu").manual_seed(cfg.seed if seed is None else seed)
         self.wte = nn.Parameter(_padded_normal(cfg.vocab_size, cfg.vocab_padded, cfg.n_embd, gen).to(device))
         self.blocks = nn.ModuleList([LlamaBlock(cfg, i, gen).to(device) for i in range(cfg.n_layer)])
         self.norm_f = nn.Parameter(torch.ones(cfg.n_embd))

@@ -19,6 +19,11 @@ def run_worker(nproc, *args, device="cpu", timeout=600):
     env = dict(os.environ, OMP_NUM_THREADS="1", NCCL_NVLS_ENABLE="0")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     line = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    log_dir = os.environ.get("CP_TEST_LOG_DIR")            # keep the complete output of a failing worker for later reading
+    if log_dir and (r.returncode != 0 or not line or not json.loads(line[-1]).get("ok")):
+        os.makedirs(log_dir, exist_ok=True)
+        with open(os.path.join(log_dir, f"worker_fail_{_PORT[0]}.log"), "w") as f:
+            f.write(" ".join(cmd) + "\n--- stdout\n" + r.stdout + "\n--- stderr\n" + r.stderr)
     assert r.returncode == 0 and line, f"worker failed rc={r.returncode}\nstdout:\n{r.stdout[-3000:]}\nstderr:\n{r.stderr[-3000:]}"
     res = json.loads(line[-1])
     assert res["ok"], res
