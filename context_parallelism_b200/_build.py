@@ -103,8 +103,9 @@ def build(verbose: bool = False, ptxas_v: bool = False, force: bool = False) -> 
     link = [f"{cuda}/bin/nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_PATH),
             *map(str, objs), "-lcudart", "-lpthread", "-ldl"]
     if nccl_lib:
-        # libnccl is resolved at run time from the PyTorch wheel (already loaded by torch); record the rpath too.
-        link += ["-Xlinker", f"-rpath={nccl_lib}"]
+        # the native process group (csrc/runtime/process_group.cpp) calls NCCL: link the copy shipped inside the
+        # PyTorch wheel (the one torch itself loads) and record its directory as rpath
+        link += ["-L", nccl_lib, "-l:libnccl.so.2", "-Xlinker", f"-rpath={nccl_lib}"]
     r = subprocess.run(link, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed: {' '.join(link)}\n{r.stdout}\n{r.stderr}")

@@ -74,7 +74,7 @@ KNOWN_ENV = {
     "CP_RING_SIZE", "CP_HYBRID_GQA",
     # this framework's additions
     "CP_FUSED", "CP_WATCHDOG_S", "CP_NVLS", "CP_GRAD_BUCKET_MB", "CP_DKV_MODE", "CP_SHARD_OPTIM", "CP_AR_CTAS",
-    "CP_FUSED_HYBRID_ULYSSES", "CP_LOAD_BALANCE", "CP_INIT_DEVICE", "CP_TEST_LOG_DIR",
+    "CP_FUSED_HYBRID_ULYSSES", "CP_LOAD_BALANCE", "CP_INIT_DEVICE", "CP_TEST_LOG_DIR", "CP_NATIVE_PG",
 }
 
 

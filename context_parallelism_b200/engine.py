@@ -43,6 +43,15 @@ class TrainEngine:
         if device.type == "cuda" and self.cp.cp_size > 1 and cfg.rotator == "fused":
             from .parallel.fused import FusedComm
             self.cp.fused = FusedComm.create(cfg, self.cp, device)
+        self.native_pg = None
+        import os
+        if (device.type == "cuda" and self.cp.ring_size > 1 and cfg.rotator == "p2p" and self.cp.ring_group is not None
+                and os.environ.get("CP_NATIVE_PG", "1") != "0"):
+            # the NCCL baseline ring hops through the native process group: a communicator and a stream of its own
+            from .parallel import rotators
+            from .parallel.process_group import NativeProcessGroup
+            self.native_pg = NativeProcessGroup.create(self.cp.ring_group, cfg.watchdog_s, True, device)
+            rotators.NATIVE_GROUPS[id(self.cp.ring_group)] = self.native_pg
         if cfg.family == "gpt2":
             from .models.gpt2 import GPT2
             self.model = GPT2(cfg, self.cp, device)
@@ -152,6 +161,12 @@ class TrainEngine:
             nv.status_for(self.device).check("train step")
 
     def close(self) -> None:
+        if self.native_pg is not None:
+            from .parallel import rotators
+            torch.cuda.synchronize(self.device)
+            rotators.NATIVE_GROUPS.pop(id(self.cp.ring_group), None)
+            self.native_pg.close()
+            self.native_pg = None
         if self.cp.fused is not None:
             self.cp.fused.close()
             self.cp.fused = None

@@ -25,6 +25,26 @@ class _Handle:
         return self.recv
 
 
+class _NativeHandle:
+    """Handle of a hop on the native process group: the consumer's stream waits on the device for the work's event
+    (``Work::streamWait`` of the reference, process_group/CpuSync_fixed.hpp:174-187); the send buffer is kept alive
+    until then."""
+
+    def __init__(self, work, recv, keep):
+        self.work, self.recv, self.keep = work, recv, keep
+
+    def wait(self) -> torch.Tensor:
+        self.work.stream_wait(torch.cuda.current_stream(self.recv.device))
+        self.recv.record_stream(torch.cuda.current_stream(self.recv.device))
+        self.work.close()
+        self.keep = None
+        return self.recv
+
+
+# torch group (by id) -> native process group with a dedicated ring communicator (registered by CPContext on CUDA)
+NATIVE_GROUPS = {}
+
+
 class P2PRotator:
     name = "p2p"
 
@@ -33,12 +53,19 @@ class P2PRotator:
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
         ranks = dist.get_process_group_ranks(group)
+        self.reverse = reverse
         step = -1 if reverse else 1
         self.next = ranks[(self.rank + step) % self.size]
         self.prev = ranks[(self.rank - step) % self.size]
 
     def exchange(self, buf: torch.Tensor) -> _Handle:
         recv = torch.empty_like(buf)
+        native = NATIVE_GROUPS.get(id(self.group)) if buf.is_cuda else None
+        if native is not None:
+            step = -1 if self.reverse else 1
+            buf = buf.contiguous()
+            w = native.sendrecv(buf, recv, (self.rank + step) % self.size, (self.rank - step) % self.size)
+            return _NativeHandle(w, recv, buf)
         ops = [dist.P2POp(dist.isend, buf, self.next, self.group), dist.P2POp(dist.irecv, recv, self.prev, self.group)]
         return _Handle(dist.batch_isend_irecv(ops), recv)
 

@@ -21,6 +21,7 @@
 // gqa_fused_rope_v2 (context_parallel/GQA_fused_fwd_sm103_cp.cu:117-281).
 #include "common.cuh"
 #include <stdio.h>
+#include <stdlib.h>
 #include "host_utils.h"
 #include "ring_copy.cuh"
 
@@ -31,6 +32,8 @@ constexpr int FA_BK = 128;
 constexpr int FA_THREADS = 320;
 constexpr int FA_KSTAGES = 3;      // K is wanted one tile ahead of V (the next score tile overlaps the softmax of this one)
 constexpr int FA_VSTAGES = 2;
+constexpr int FA_POLY_D64 = 3;     // default share (of 8) of the exponentials taken off the special-function unit
+constexpr int FA_POLY_D128 = 2;
 
 struct FwdParams {
   int B, Tq, Tk, Hq, Hkv;
@@ -94,7 +97,35 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int value, volatil
   return false;
 }
 
-template <int D>
+// exp2 of two floats on the FMA and integer pipes instead of the special-function unit: x = n + f with n = round(x),
+// f in [-0.5, 0.5]; 2^f from a cubic (maximum relative error 7.6e-5, far below the bf16 rounding P gets anyway);
+// the result's exponent field is then advanced by n with an integer add.  The special-function unit delivers 16
+// exponentials per clock per SM, a query-key tile needs 16384 of them, and that (not the tensor pipe) is what bounds
+// this kernel at head_dim 64; sending a share of the columns through this routine moves the limit.
+// Valid for x <= 100; arguments below -126 are clamped (the result is then 2^-126 instead of a denormal or zero).
+__device__ __forceinline__ uint64_t exp2_poly_f32x2(uint64_t x2) {
+  float x0, x1;
+  unpack_f32x2(x2, x0, x1);
+  x0 = fmaxf(x0, -126.f); x1 = fmaxf(x1, -126.f);
+  x2 = pack_f32x2(x0, x1);
+  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);          // 1.5 * 2^23: adding it rounds to an integer
+  const uint64_t t = add_f32x2(x2, magic);
+  const uint64_t r = add_f32x2(t, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f = fma_f32x2(r, pack_f32x2(-1.f, -1.f), x2);
+  uint64_t p = fma_f32x2(f, pack_f32x2(0.05520550534129143f, 0.05520550534129143f), pack_f32x2(0.24261397123336792f, 0.24261397123336792f));
+  p = fma_f32x2(p, f, pack_f32x2(0.6932547688484192f, 0.6932547688484192f));
+  p = fma_f32x2(p, f, pack_f32x2(0.9999276995658875f, 0.9999276995658875f));
+  float t0, t1, p0, p1;
+  unpack_f32x2(t, t0, t1);
+  unpack_f32x2(p, p0, p1);
+  // the low mantissa bits of t hold n in two's complement; shifted into the exponent field they add n to p's exponent
+  p0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+  return pack_f32x2(p0, p1);
+}
+
+// POLY: of the 8 column pairs of every 16-column group, the last POLY take exp2_poly_f32x2 and the others ex2.approx.
+template <int D, int POLY>
 __global__ void __launch_bounds__(FA_THREADS, (D == 64 ? 2 : 1))
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, FwdParams p) {
@@ -361,10 +392,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           uint32_t pk[8];
 #pragma unroll
           for (int i = 0; i < 16; i += 2) {
-            float x0, x1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[ch][i]), __uint_as_float(sv[ch][i + 1])), c2, m2), x0, x1);
-            const float p0 = ex2f(x0), p1 = ex2f(x1);
-            l2 = add_f32x2(l2, pack_f32x2(p0, p1));
+            float p0, p1;
+            const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sv[ch][i]), __uint_as_float(sv[ch][i + 1])), c2, m2);
+            if ((i >> 1) >= 8 - POLY) {                      // resolved at compile time (the loop is unrolled)
+              const uint64_t p2 = exp2_poly_f32x2(x2);
+              l2 = add_f32x2(l2, p2);
+              unpack_f32x2(p2, p0, p1);
+            } else {
+              float x0, x1;
+              unpack_f32x2(x2, x0, x1);
+              p0 = ex2f(x0); p1 = ex2f(x1);
+              l2 = add_f32x2(l2, pack_f32x2(p0, p1));
+            }
             pk[i >> 1] = pack_bf16(p0, p1);
           }
           tmem_st8(t_lane + P_COL + half * 32 + ch * 8, pk);
@@ -489,15 +528,34 @@ extern "C" int cpb_flash_fwd(const void* q, const void* k, const void* v, void* 
   if (p.n_copy > 0 && ready == nullptr) return set_error(CPB_ERR_ARG, "flash_fwd: copy CTAs need ready flags");
   const int G = Hq / Hkv;
   dim3 grid(p.n_copy + ((Tq + FA_BQ - 1) / FA_BQ) * G, Hkv, B);
+  // Share of the exponentials computed on the FMA pipe (column pairs out of 8); CPB_FWD_POLY overrides the tuned
+  // default and is read once.
+  static const int poly = [] { const char* e = getenv("CPB_FWD_POLY"); return e ? atoi(e) : -1; }();
+#define CPB_FWD_LAUNCH(DD, PP)                                                                                         \
+  do {                                                                                                                 \
+    static bool cfg = false;                                                                                           \
+    if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel<DD, PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<DD>::TOTAL)); cfg = true; } \
+    flash_fwd_kernel<DD, PP><<<grid, FA_THREADS, FwdSmem<DD>::TOTAL, stream>>>(tq, tk, tv, p);                         \
+  } while (0)
   if (D == 64) {
-    static bool cfg = false;
-    if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::TOTAL)); cfg = true; }
-    flash_fwd_kernel<64><<<grid, FA_THREADS, FwdSmem<64>::TOTAL, stream>>>(tq, tk, tv, p);
+    switch (poly < 0 ? FA_POLY_D64 : poly) {
+      case 0: CPB_FWD_LAUNCH(64, 0); break;
+      case 1: CPB_FWD_LAUNCH(64, 1); break;
+      case 2: CPB_FWD_LAUNCH(64, 2); break;
+      case 4: CPB_FWD_LAUNCH(64, 4); break;
+      case 5: CPB_FWD_LAUNCH(64, 5); break;
+      default: CPB_FWD_LAUNCH(64, 3); break;
+    }
   } else {
-    static bool cfg = false;
-    if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::TOTAL)); cfg = true; }
-    flash_fwd_kernel<128><<<grid, FA_THREADS, FwdSmem<128>::TOTAL, stream>>>(tq, tk, tv, p);
+    switch (poly < 0 ? FA_POLY_D128 : poly) {
+      case 0: CPB_FWD_LAUNCH(128, 0); break;
+      case 1: CPB_FWD_LAUNCH(128, 1); break;
+      case 3: CPB_FWD_LAUNCH(128, 3); break;
+      case 4: CPB_FWD_LAUNCH(128, 4); break;
+      default: CPB_FWD_LAUNCH(128, 2); break;
+    }
   }
+#undef CPB_FWD_LAUNCH
 #ifdef CPB_FWD_PROF
   {
     long long h[64];

@@ -40,6 +40,8 @@ def main():
     ap.add_argument("--share-slots", type=int, default=0)
     ap.add_argument("--lb", type=int, default=1)
     ap.add_argument("--recompute-k", type=int, default=0)
+    ap.add_argument("--pg-test", type=int, default=0)
+    ap.add_argument("--fcp-test", type=int, default=0)
     a = ap.parse_args()
 
     from context_parallelism_b200.config import Config
@@ -47,6 +49,13 @@ def main():
     from context_parallelism_b200.parallel.mesh import init_distributed
     rank, world, local = init_distributed("nccl" if a.device == "cuda" else "gloo", timeout_s=120)
     dev = torch.device("cuda", local) if a.device == "cuda" else torch.device("cpu")
+    if a.pg_test:
+        ok = native_pg_test(rank, world, dev)
+        if rank == 0:
+            print(json.dumps({"ok": ok, "pg_test": True, "world": world}))
+        dist.barrier()
+        dist.destroy_process_group()
+        sys.exit(0 if ok else 1)
     cp = a.cp or world
     head_dim = 64 if a.device == "cuda" else 16
     kw = dict(n_embd=4 * head_dim, n_layer=2, n_head=4, n_kv_head=a.kv if a.family == "llama" else 4, head_dim=head_dim,
@@ -61,6 +70,14 @@ def main():
     dp = world // cp
     dp_rank = eng.cp.dp_rank
     ok, msgs = True, []
+    if a.fcp_test:
+        res = forward_cp_test(eng, cfg, dev)
+        if rank == 0:
+            print(json.dumps(res))
+        eng.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        sys.exit(0 if res["ok"] else 1)
     op = None
     if a.op_parity and eng.cp.fused is not None and a.mode in ("ring", "ulysses"):
         op = op_parity(eng, cfg, dev)
@@ -104,6 +121,91 @@ def main():
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if res.item() > 0.5 else 1)
+
+
+def forward_cp_test(eng, cfg, dev):
+    """``forward_cp`` in its four sharding modes against the dense oracle: full-sequence inputs sharded inside
+    (``pre_sharded=False``) and/or the output gathered back (``unshard=True``), forward and all three gradients
+    (the reference's op-level parity, Tests/cp_ulysses_parity.cpp:650-651, Tests/cp_rope_standin_parity.cpp:117-153)."""
+    from context_parallelism_b200.ops import reference as ref
+    attn, cp = eng.model.attn, eng.cp
+    B, T, Hq, Hkv, D = cfg.B, cfg.T, cfg.n_head, cfg.n_kv_head, cfg.head_dim
+    dt = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    gen = torch.Generator().manual_seed(5)
+    q, k, v, do = (torch.randn(B, T, h, D, generator=gen).to(dev).to(dt) for h in (Hq, Hkv, Hkv, Hq))
+    scale = D ** -0.5
+    o_ref, lse_ref = ref.attention_dense(q.float(), k.float(), v.float(), scale, None, None, True)
+    g_ref = ref.attention_dense_bwd(q.float(), k.float(), v.float(), o_ref, lse_ref, do.float(), scale, None, None, True)
+    pos = cp.local_positions(T).to(dev)
+    worst = 1.0
+
+    def cos(x, y):
+        x, y = x.double().flatten(), y.double().flatten()
+        return float((x @ y) / (x.norm() * y.norm() + 1e-30))
+    for pre_sharded in (False, True):
+        for unshard in (False, True):
+            sel = (lambda t: t.index_select(1, pos).contiguous()) if pre_sharded else (lambda t: t.clone())
+            qi, ki, vi = (sel(t).requires_grad_() for t in (q, k, v))
+            o = attn.forward_cp(qi, ki, vi, unshard=unshard, pre_sharded=pre_sharded)
+            o.backward(do if unshard else do.index_select(1, pos))
+            want_o = o_ref if unshard else o_ref.index_select(1, pos)
+            cs = [cos(o, want_o)]
+            for got, want in zip((qi.grad, ki.grad, vi.grad), g_ref):
+                cs.append(cos(got, want.index_select(1, pos) if pre_sharded else want))
+            worst = min(worst, *cs)
+    t = torch.tensor([worst], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    lim = 0.995 if dev.type == "cuda" else 0.99999
+    return {"ok": bool(t.item() > lim), "worst_cos": float(t.item()), "fcp_test": True, "mode": cfg.attn_mode}
+
+
+def native_pg_test(rank, world, dev):
+    """Every collective of the native NCCL process group against its definition, the ring hop on the dedicated
+    communicator, a communicator split, and the work handle's three ways of waiting."""
+    from context_parallelism_b200.parallel.process_group import NativeProcessGroup
+    from context_parallelism_b200.parallel.work import DONE
+    torch.cuda.set_device(dev)
+    pg = NativeProcessGroup.create(None, timeout_s=60.0, with_ring=True, device=dev)
+    ok = pg.world == world and pg.rank == rank and pg.async_error() == 0
+    cur = torch.cuda.current_stream(dev)
+    x = torch.full((1000,), float(rank + 1), device=dev)
+    w = pg.all_reduce(x, "sum"); w.stream_wait(cur); w.close()
+    ok &= bool((x == world * (world + 1) / 2).all())
+    y = torch.full((64,), float(rank), device=dev, dtype=torch.bfloat16)
+    w = pg.broadcast(y, world - 1)
+    ok &= w.wait() == DONE                               # host-side polling wait with the deadline
+    w.close()
+    ok &= bool((y == world - 1).all())
+    g = torch.empty(world * 8, device=dev)
+    w = pg.all_gather(torch.full((8,), float(rank), device=dev), g); w.stream_wait(cur); w.close()
+    ok &= bool((g.view(world, 8)[:, 0] == torch.arange(world, device=dev)).all())
+    rs = torch.empty(4, device=dev)
+    w = pg.reduce_scatter(torch.arange(world * 4, device=dev, dtype=torch.float32), rs, "avg"); w.stream_wait(cur); w.close()
+    ok &= bool((rs == torch.arange(rank * 4, rank * 4 + 4, device=dev)).all())
+    send = (torch.arange(world * 3, device=dev) + 100 * rank).float()
+    recv = torch.empty_like(send)
+    w = pg.all_to_all(send, recv); w.stream_wait(cur); w.close()
+    want = torch.cat([torch.arange(rank * 3, rank * 3 + 3, device=dev).float() + 100 * r for r in range(world)])
+    ok &= bool((recv == want).all())
+    hop = torch.empty(16, device=dev)
+    w = pg.sendrecv(torch.full((16,), float(rank), device=dev), hop, (rank + 1) % world, (rank - 1) % world)
+    w.stream_wait(cur)
+    ok &= w.query() in (0, 1)
+    w.close()
+    ok &= bool((hop == (rank - 1) % world).all())
+    if world >= 2:
+        half = pg.split(rank % 2, rank // 2, (world + 1 - rank % 2) // 2, rank // 2)        # even / odd ranks
+        z = torch.ones(4, device=dev)
+        w = half.all_reduce(z, "sum"); w.stream_wait(cur); w.close()
+        ok &= bool((z == half.world).all())
+        torch.cuda.synchronize(dev)
+        half.close()
+    torch.cuda.synchronize(dev)
+    ok &= pg.async_error() == 0
+    pg.close()
+    t = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item() > 0.5)
 
 
 def op_parity(eng, cfg, dev):

@@ -42,6 +42,13 @@ def test_ring_ws2_variants(extra):
     run_worker(2, "--mode", "ring", "--rotator", "p2p", "--tol", 1e-4, *extra)
 
 
+@pytest.mark.parametrize("mode,rot,kv", [("ring", "p2p", 2), ("ring", "allgather", 4), ("ulysses", "alltoall", 2), ("ulysses", "alltoall", 1)])
+def test_forward_cp_shard_and_unshard_ws2(mode, rot, kv):
+    """forward_cp(unshard, pre_sharded) in all four combinations, forward and gradients, against the dense oracle."""
+    res = run_worker(2, "--mode", mode, "--rotator", rot, "--kv", kv, "--fcp-test", 1)
+    assert res["fcp_test"] and res["worst_cos"] > 0.99999
+
+
 def test_ring_ws4_gpt2():
     run_worker(4, "--mode", "ring", "--rotator", "p2p", "--family", "gpt2", "--tol", 1e-4)
 

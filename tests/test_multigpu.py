@@ -30,6 +30,12 @@ def test_ulysses_2gpu(rotator, kv, extra):
     run_worker(2, "--mode", "ulysses", "--rotator", rotator, "--kv", kv, "--T", 1024, "--tol", TOL, *extra, device="cuda")
 
 
+def test_native_process_group_2gpu():
+    """The C++ NCCL process group: collectives, ring hop on the dedicated communicator, split, work handles."""
+    res = run_worker(2, "--pg-test", 1, device="cuda")
+    assert res["pg_test"]
+
+
 def test_ring_fused_gpt2_recompute_2gpu():
     run_worker(2, "--mode", "ring", "--rotator", "fused", "--family", "gpt2", "--T", 1024, "--tol", TOL,
                "--recompute", "selective", device="cuda")
