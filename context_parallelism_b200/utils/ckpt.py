@@ -182,6 +182,22 @@ class CheckpointManager:
                 pass
         return p
 
+    def seed_run_from(self, src_run: int, dst_run: int) -> int:
+        """Start ``dst_run`` from the newest checkpoint of ``src_run``: the file is copied under the new run's name
+        (same step), so that resuming ``dst_run`` continues training from those weights and optimiser moments.  Does
+        nothing if ``dst_run`` already has a checkpoint.  Returns the step of ``dst_run``'s newest checkpoint."""
+        import shutil
+        runs = self.list_runs()
+        if runs.get(dst_run):
+            return runs[dst_run][-1]
+        if not runs.get(src_run):
+            raise FileNotFoundError(f"run {src_run} has no checkpoint under {self.root}")
+        step = runs[src_run][-1]
+        tmp = self.path(dst_run, step) + ".tmp"
+        shutil.copyfile(self.path(src_run, step), tmp)
+        os.replace(tmp, self.path(dst_run, step))
+        return step
+
     def load_latest(self, run: int, model, flat, opt) -> Tuple[int, float]:
         """Load the newest checkpoint of ``run`` on every rank; returns ``(step, loss)`` or ``(0, nan)``."""
         steps = self.list_runs().get(run, [])

@@ -92,3 +92,54 @@ def _parse(argv):
                      ("--timeout", {"type": float}), ("--port", {"type": int, "default": 29651}), ("--out", {}), ("--env", {"action": "append", "default": []})):
         ap.add_argument(name, **kw)
     return ap.parse_args(argv)
+
+
+def test_progressive_pipeline_resumes_from_done_markers(tmp_path):
+    """Search -> fine-tune -> eval for one extension stage on a tiny CPU model; a second run of the same command skips
+    every finished sub-step; the GPU-idle poll returns once usage drops."""
+    from context_parallelism_b200.experiments import pipeline as P
+    arch = ["CP_N_EMBD=32", "CP_N_LAYER=1", "CP_N_HEAD=4", "CP_N_KVHEAD=2", "CP_HEAD_DIM=8", "CP_FFN=64", "CP_VOCAB=97", "CP_SYNTHETIC=1",
+            "CP_ATTN_MODE=ring", "CP_ROTATOR=p2p"]
+    ck = tmp_path / "ck"
+    env = dict(os.environ, **dict(e.split("=") for e in arch), CP_CKPT="1", CP_CKPT_DIR=str(ck), CP_LOG_DIR=str(tmp_path), CP_T="32", CP_B="1",
+               CP_GLOBAL_BATCH="32", CP_MAX_STEPS="2", CP_CKPT_FREQ="2", CP_VAL_FREQ="0")
+    r = subprocess.run([sys.executable, "-m", "context_parallelism_b200.trainers.llama_cp"], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    argv = ["progressive", "--state-dir", str(tmp_path / "state"), "--ckpt-dir", str(ck), "--base-t", "32", "--stages", "2", "--head-dim", "8",
+            "--population", "4", "--generations", "2", "--search-windows", "1", "--eval-windows", "1", "--ft-steps", "2", "--ckpt-freq", "2",
+            "--rewarmup", "1", "--timeout", "300", "--port", "29790"] + sum((["--env", e] for e in arch), [])
+    saved = dict(os.environ)
+    try:
+        ap_args = _pipeline_args(argv)
+        res = P.progressive(ap_args)
+        assert res["ran"] == ["search_s2", "finetune_s2", "eval_s2"] and res["skipped"] == []
+        assert (tmp_path / "state" / "eval_s2.done").exists() and (tmp_path / "state" / "ppl_prog_s2.csv").exists()
+        assert (ck / "blumodelcp_run100_step_4.ckpt").exists()                  # base step 2 + 2 fine-tune steps, in the stage's own run
+        res2 = P.progressive(_pipeline_args(argv))
+        assert res2["ran"] == [] and res2["skipped"] == ["search_s2", "finetune_s2", "eval_s2"]
+    finally:
+        os.environ.clear()
+        os.environ.update(saved)
+    used = iter([[9000, 10], [100, 10]])
+    assert P.wait_for_idle_gpus(500, poll_s=0.01, query=lambda: next(used))
+    assert not P.wait_for_idle_gpus(5, poll_s=0.01, max_wait_s=0.05, query=lambda: [100])
+
+
+def _pipeline_args(argv):
+    from context_parallelism_b200.experiments import pipeline as P
+    import argparse
+    holder = {}
+    real = argparse.ArgumentParser.parse_args
+
+    def grab(self, args=None, namespace=None):
+        holder["a"] = real(self, args, namespace)
+        raise SystemExit(0)
+    argparse.ArgumentParser.parse_args = grab
+    try:
+        try:
+            P.main(argv)
+        except SystemExit:
+            pass
+    finally:
+        argparse.ArgumentParser.parse_args = real
+    return holder["a"]
