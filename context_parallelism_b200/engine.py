@@ -58,6 +58,12 @@ class TrainEngine:
         else:
             from .models.llama import Llama
             self.model = Llama(cfg, self.cp, device)
+        if device.type == "cuda":
+            from .ops import attention as _A
+            _A.FP32_ACCURATE = bool(cfg.attn_fp32)
+            if cfg.attn_fp32 and self.cp.cp_size > 1 and not (cfg.attn_mode == "ulysses" and cfg.rotator != "fused"):
+                raise ValueError("ATTN_FP32=1 (fp32-accurate attention for parity runs) is supported on one GPU and for Ulysses "
+                                 "with an NCCL rotator (CP_ROTATOR=alltoall); the other paths are built on the tensor-core kernels")
         bf16 = cfg.dtype == "bf16" and device.type == "cuda"
         if device.type == "cuda" and not bf16:
             raise ValueError("the CUDA kernels compute in bf16; CP_DTYPE=fp32 is the CPU oracle path")

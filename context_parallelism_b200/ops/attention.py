@@ -100,12 +100,60 @@ class _FlashAttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None
 
 
+# ATTN_FP32=1: differentiable attention goes through the fp32-accurate CUDA-core kernels (parity runs); set by the engine.
+FP32_ACCURATE = False
+
+
+def _fp32_args(q, k, B, Tq, Tk, Hq, Hkv, D, scale, causal, k_off, q_pos):
+    qs, ks = _strides(q), _strides(k)
+    return (nv.i(B), nv.i(Tq), nv.i(Tk), nv.i(Hq), nv.i(Hkv), nv.i(D), nv.l(qs[0]), nv.l(qs[1]), nv.l(qs[2]), nv.l(ks[0]), nv.l(ks[1]),
+            nv.l(ks[2]), nv.f(scale), nv.i(causal), nv.i(k_off), nv.ptr(q_pos), nv.stream_ptr(q.device))
+
+
+class _AttnFp32Fn(torch.autograd.Function):
+    """The fp32-accurate variant (``csrc/kernels/attention_fp32.cu``; the reference's ``ATTN_FP32`` scalar kernel,
+    context_parallel/FusedSDPAOp.h:134-163): bf16 inputs, every intermediate in fp32, fp32 gradients rounded once."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, causal, q_pos, k_off):
+        B, Tq, Hq, D = q.shape
+        Tk, Hkv = k.shape[1], k.shape[2]
+        q = q if _ok_layout(q) else q.contiguous()
+        k = k if _ok_layout(k) else k.contiguous()
+        if not _ok_layout(v) or v.stride() != k.stride():
+            k, v = k.contiguous(), v.contiguous()
+        qp = None if q_pos is None else q_pos.to(torch.int32)
+        out = torch.empty((B, Tq, Hq, D), dtype=torch.float32, device=q.device)
+        lse = torch.empty((B, Hq, Tq), dtype=torch.float32, device=q.device)
+        nv.call("attn_fp32_fwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(out), nv.ptr(lse),
+                *_fp32_args(q, k, B, Tq, Tk, Hq, Hkv, D, scale, causal, k_off, qp))
+        ctx.save_for_backward(q, k, v, out, lse, qp)
+        ctx.scale, ctx.causal, ctx.k_off = scale, causal, k_off
+        ctx.mark_non_differentiable(lse)
+        return out.to(q.dtype), lse
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        q, k, v, out, lse, qp = ctx.saved_tensors
+        B, Tq, Hq, D = q.shape
+        Tk, Hkv = k.shape[1], k.shape[2]
+        do = dout.float().contiguous()
+        dq = torch.empty((B, Tq, Hq, D), dtype=torch.float32, device=q.device)
+        dk = torch.zeros((B, Tk, Hkv, D), dtype=torch.float32, device=q.device)
+        dv = torch.zeros_like(dk)
+        nv.call("attn_fp32_bwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(out), nv.ptr(lse), nv.ptr(do), nv.ptr(dq), nv.ptr(dk), nv.ptr(dv),
+                *_fp32_args(q, k, B, Tq, Tk, Hq, Hkv, D, ctx.scale, ctx.causal, ctx.k_off, qp))
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None, None
+
+
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None,
                     causal: bool = True, q_pos: Optional[torch.Tensor] = None, k_off: int = 0
                     ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Differentiable attention; see the module docstring for layouts and masking."""
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
+    if q.is_cuda and FP32_ACCURATE:
+        return _AttnFp32Fn.apply(q, k, v, scale, causal, q_pos, k_off)
     if q.is_cuda:
         return _FlashAttnFn.apply(q, k, v, scale, causal, q_pos, k_off)
     Tk = k.shape[1]

@@ -249,3 +249,31 @@ def test_flash_autograd_positions():
     assert_close(out.float().cpu(), want, cos=0.999, name="out")
     for a, b_, n in ((q, Q, "dq"), (k, K, "dk"), (v, V, "dv")):
         assert_close(a.grad.float().cpu(), b_.grad, cos=0.995, name=n)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(64, 4, 2), (128, 2, 1), (32, 4, 4)])
+def test_attention_fp32_accurate_variant(D, Hq, Hkv):
+    """ATTN_FP32 kernels: fp32 arithmetic on bf16 inputs reproduces the dense oracle far more tightly than the tensor-core
+    path (forward cos > 0.99999 and 1e-3 relative, gradients cos > 0.9999: the reference's fp32 bars)."""
+    from context_parallelism_b200.ops import attention as A
+    from context_parallelism_b200.ops import reference as ref
+    torch.manual_seed(3)
+    B, T = 2, 200
+    q, k, v, do = (torch.randn(B, T, h, D, device=dev()).bfloat16() for h in (Hq, Hkv, Hkv, Hq))
+    scale = D ** -0.5
+    qpos = torch.arange(T, device=dev()) + 7
+    A.FP32_ACCURATE = True
+    try:
+        qi, ki, vi = (t.clone().requires_grad_() for t in (q, k, v))
+        o, lse = A.flash_attention(qi, ki, vi, scale, True, qpos, 5)
+        o.backward(do)
+    finally:
+        A.FP32_ACCURATE = False
+    kp = torch.arange(5, 5 + T, device=dev())
+    o_ref, lse_ref = ref.attention_dense(q.float(), k.float(), v.float(), scale, qpos, kp, True)
+    g_ref = ref.attention_dense_bwd(q.float(), k.float(), v.float(), o_ref, lse_ref, do.float(), scale, qpos, kp, True)
+    check_status()
+    assert_close(o.float(), o_ref, cos=0.99999, rel=1e-2, name="fp32 attn out")       # the bf16 rounding of the output remains
+    assert_close(lse, lse_ref, cos=0.999999, rel=1e-4, name="fp32 attn lse")
+    for got, want, nm in zip((qi.grad, ki.grad, vi.grad), g_ref, ("dq", "dk", "dv")):
+        assert_close(got.float(), want, cos=0.9999, rel=2e-2, name="fp32 attn " + nm)
