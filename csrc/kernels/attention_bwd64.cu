@@ -45,6 +45,7 @@ namespace cpb {
 constexpr int B64_T = 128;
 constexpr int B64_D = 64;
 constexpr int B64_THREADS = 448;
+constexpr int B64_POLY = 0;        // share (of 8) of the exponentials computed on the FMA pipe: measured neutral (846 to 855 TFLOP/s for 0..4), kept off
 
 static __device__ long long g_bwd64_prof[16 + 32 * 8];
 
@@ -109,6 +110,9 @@ __device__ __forceinline__ void red_add_v4_64(float* addr, float a, float b, flo
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+// POLY: of the 8 column pairs of every 16-column group of an unmasked tile, the last POLY take their exponentials from
+// exp2_poly_f32x2 (FMA pipe) and the others from ex2.approx (special-function unit).
+template <int POLY>
 __global__ void __launch_bounds__(B64_THREADS, 1)
 flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -331,11 +335,19 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_arrive_warp(s_consumed);                         // the next score tile may overwrite S'^T
       uint32_t pk[32];                                  // P^T of this thread's 64 queries, bf16 pairs
       if (!need_mask) {
+        const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2);
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
-          for (int j = 0; j < 16; j += 2)
-            pk[ch * 8 + (j >> 1)] = pack_bf16(ex2f(__uint_as_float(sv[ch][j]) * p.scale_log2), ex2f(__uint_as_float(sv[ch][j + 1]) * p.scale_log2));
+          for (int j = 0; j < 16; j += 2) {
+            if ((j >> 1) >= 8 - POLY) {                 // resolved at compile time (the loops are unrolled)
+              float p0, p1;
+              unpack_f32x2(exp2_poly_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(sv[ch][j]), __uint_as_float(sv[ch][j + 1])), c2)), p0, p1);
+              pk[ch * 8 + (j >> 1)] = pack_bf16(p0, p1);
+            } else {
+              pk[ch * 8 + (j >> 1)] = pack_bf16(ex2f(__uint_as_float(sv[ch][j]) * p.scale_log2), ex2f(__uint_as_float(sv[ch][j + 1]) * p.scale_log2));
+            }
+          }
       } else {
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch)
@@ -587,18 +599,32 @@ extern "C" int cpb_flash_bwd64(const void* q, const void* k, const void* v, cons
   p.aug_l = (const __nv_bfloat16*)aug_l; p.aug_d = (const __nv_bfloat16*)aug_d; p.q_pos = q_pos;
   p.dk = dk; p.dv = dv; p.dkv_mode = dkv_mode; p.status = status;
   p.route_k = route_k; p.route_v = route_v; p.route_rows = route_rows; p.route_tl = route_tl;
-  const char* e = getenv("CPB_BWD_SKIP_DQ");
-  p.debug_skip_dq = (e != nullptr && e[0] == '1');
+  // diagnostic switches and the tuning knob are read once per process, not per launch
+  static const bool skip_dq = [] { const char* e = getenv("CPB_BWD_SKIP_DQ"); return e != nullptr && e[0] == '1'; }();
+  static const bool want_prof = [] { const char* e = getenv("CPB_BWD_PROF"); return e != nullptr && e[0] == '1'; }();
+  static const int poly = [] { const char* e = getenv("CPB_BWD64_POLY"); return e ? atoi(e) : B64_POLY; }();
+  p.debug_skip_dq = skip_dq;
   p.prof = nullptr;
-  const char* pe = getenv("CPB_BWD_PROF");
-  if (pe != nullptr && pe[0] == '1') {
+  if (want_prof) {
     void* sym = nullptr;
     if (cudaGetSymbolAddress(&sym, g_bwd64_prof) == cudaSuccess) { p.prof = (long long*)sym; cudaMemsetAsync(sym, 0, sizeof(long long) * (16 + 32 * 8), stream); }
   }
-  static bool cfg = false;
-  if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_bwd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd64Smem::TOTAL)); cfg = true; }
   dim3 grid((Tk + B64_T - 1) / B64_T, Hkv, B);
-  flash_bwd64_kernel<<<grid, B64_THREADS, Bwd64Smem::TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);
+#define CPB_BWD64_LAUNCH(PP)                                                                                            \
+  do {                                                                                                                  \
+    static bool cfg = false;                                                                                            \
+    if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_bwd64_kernel<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd64Smem::TOTAL)); cfg = true; } \
+    flash_bwd64_kernel<PP><<<grid, B64_THREADS, Bwd64Smem::TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);                   \
+  } while (0)
+  switch (poly) {
+    case 0: CPB_BWD64_LAUNCH(0); break;
+    case 1: CPB_BWD64_LAUNCH(1); break;
+    case 2: CPB_BWD64_LAUNCH(2); break;
+    case 4: CPB_BWD64_LAUNCH(4); break;
+    case 5: CPB_BWD64_LAUNCH(5); break;
+    default: CPB_BWD64_LAUNCH(3); break;
+  }
+#undef CPB_BWD64_LAUNCH
   if (p.prof != nullptr) {
     long long h[16 + 32 * 8];
     cudaStreamSynchronize(stream);

@@ -32,7 +32,7 @@ constexpr int FA_BK = 128;
 constexpr int FA_THREADS = 320;
 constexpr int FA_KSTAGES = 3;      // K is wanted one tile ahead of V (the next score tile overlaps the softmax of this one)
 constexpr int FA_VSTAGES = 2;
-constexpr int FA_POLY_D64 = 3;     // default share (of 8) of the exponentials taken off the special-function unit
+constexpr int FA_POLY_D64 = 0;     // default share (of 8) of the exponentials taken off the special-function unit
 constexpr int FA_POLY_D128 = 2;
 
 struct FwdParams {
@@ -95,33 +95,6 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int value, volatil
   *abort_flag = 1;
   report(status, ST_TIMEOUT_FLAG, site, value);
   return false;
-}
-
-// exp2 of two floats on the FMA and integer pipes instead of the special-function unit: x = n + f with n = round(x),
-// f in [-0.5, 0.5]; 2^f from a cubic (maximum relative error 7.6e-5, far below the bf16 rounding P gets anyway);
-// the result's exponent field is then advanced by n with an integer add.  The special-function unit delivers 16
-// exponentials per clock per SM, a query-key tile needs 16384 of them, and that (not the tensor pipe) is what bounds
-// this kernel at head_dim 64; sending a share of the columns through this routine moves the limit.
-// Valid for x <= 100; arguments below -126 are clamped (the result is then 2^-126 instead of a denormal or zero).
-__device__ __forceinline__ uint64_t exp2_poly_f32x2(uint64_t x2) {
-  float x0, x1;
-  unpack_f32x2(x2, x0, x1);
-  x0 = fmaxf(x0, -126.f); x1 = fmaxf(x1, -126.f);
-  x2 = pack_f32x2(x0, x1);
-  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);          // 1.5 * 2^23: adding it rounds to an integer
-  const uint64_t t = add_f32x2(x2, magic);
-  const uint64_t r = add_f32x2(t, pack_f32x2(-12582912.f, -12582912.f));
-  const uint64_t f = fma_f32x2(r, pack_f32x2(-1.f, -1.f), x2);
-  uint64_t p = fma_f32x2(f, pack_f32x2(0.05520550534129143f, 0.05520550534129143f), pack_f32x2(0.24261397123336792f, 0.24261397123336792f));
-  p = fma_f32x2(p, f, pack_f32x2(0.6932547688484192f, 0.6932547688484192f));
-  p = fma_f32x2(p, f, pack_f32x2(0.9999276995658875f, 0.9999276995658875f));
-  float t0, t1, p0, p1;
-  unpack_f32x2(t, t0, t1);
-  unpack_f32x2(p, p0, p1);
-  // the low mantissa bits of t hold n in two's complement; shifted into the exponent field they add n to p's exponent
-  p0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
-  p1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
-  return pack_f32x2(p0, p1);
 }
 
 // POLY: of the 8 column pairs of every 16-column group, the last POLY take exp2_poly_f32x2 and the others ex2.approx.

@@ -395,6 +395,32 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   CPB_MATH_ASM("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+// exp2 of two floats on the FMA and integer pipes instead of the special-function unit: x = n + f with n = round(x),
+// f in [-0.5, 0.5]; 2^f from a cubic (maximum relative error 7.6e-5, far below the bf16 rounding the result gets);
+// the result's exponent field is then advanced by n with an integer add.  The special-function unit delivers 16
+// exponentials per clock per SM and a 128x128 attention tile needs 16384 of them; sending a share of the columns
+// through this routine shortens the exponential phase of the attention kernels.
+// Valid for x <= 100; arguments below -126 are clamped (the result is then 2^-126 instead of a denormal or zero).
+__device__ __forceinline__ uint64_t exp2_poly_f32x2(uint64_t x2) {
+  float x0, x1;
+  unpack_f32x2(x2, x0, x1);
+  x0 = fmaxf(x0, -126.f); x1 = fmaxf(x1, -126.f);
+  x2 = pack_f32x2(x0, x1);
+  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);          // 1.5 * 2^23: adding it rounds to an integer
+  const uint64_t t = add_f32x2(x2, magic);
+  const uint64_t r = add_f32x2(t, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f = fma_f32x2(r, pack_f32x2(-1.f, -1.f), x2);
+  uint64_t p = fma_f32x2(f, pack_f32x2(0.05520550534129143f, 0.05520550534129143f), pack_f32x2(0.24261397123336792f, 0.24261397123336792f));
+  p = fma_f32x2(p, f, pack_f32x2(0.6932547688484192f, 0.6932547688484192f));
+  p = fma_f32x2(p, f, pack_f32x2(0.9999276995658875f, 0.9999276995658875f));
+  float t0, t1, p0, p1;
+  unpack_f32x2(t, t0, t1);
+  unpack_f32x2(p, p0, p1);
+  // the low mantissa bits of t hold n in two's complement; shifted into the exponent field they add n to p's exponent
+  p0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+  return pack_f32x2(p0, p1);
+}
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
 
