@@ -51,7 +51,7 @@ class Timer:
         return t[len(t) // 2]
 
 
-def bench_attention(tm, out, shapes, tflops_peak):
+def bench_attention(tm, out, shapes, tflops_peak, which="both"):
     from context_parallelism_b200.ops import attention as A
     for D, Hq, Hkv, T in shapes:
         dev = tm.dev
@@ -59,10 +59,13 @@ def bench_attention(tm, out, shapes, tflops_peak):
         k = torch.randn(1, T, Hkv, D, device=dev).bfloat16()
         v = torch.randn_like(k)
         sc = 1 / math.sqrt(D)
-        ms = tm.ms(lambda: A.flash_fwd(q, k, v, sc, True))
-        fl = 4 * T * T * Hq * D / 2
-        out.append({"kernel": "flash_fwd", "head_dim": D, "heads": f"{Hq}/{Hkv}", "T": T, "ms": ms, "tflops": fl / ms / 1e9,
-                    "frac_of_peak": fl / ms / 1e9 / tflops_peak})
+        if which in ("both", "fwd"):
+            ms = tm.ms(lambda: A.flash_fwd(q, k, v, sc, True))
+            fl = 4 * T * T * Hq * D / 2
+            out.append({"kernel": "flash_fwd", "head_dim": D, "heads": f"{Hq}/{Hkv}", "T": T, "ms": ms, "tflops": fl / ms / 1e9,
+                        "frac_of_peak": fl / ms / 1e9 / tflops_peak})
+        if which == "fwd":
+            continue
         o, lse = A.flash_fwd(q, k, v, sc, True)
         do = torch.randn_like(o)
         ms = tm.ms(lambda: A.flash_bwd(q, k, v, o, lse, do, sc, True))
@@ -158,6 +161,10 @@ def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", nargs="+", default=["attn", "gemm", "membound"], choices=["attn", "gemm", "membound"])
     ap.add_argument("--T", type=int, nargs="+", default=[16384])
+    ap.add_argument("--head-dims", type=int, nargs="+", default=[64, 128])
+    ap.add_argument("--attn-pass", default="both", choices=["both", "fwd", "bwd"])
+    ap.add_argument("--rows", type=int, default=131072, help="token rows of the memory-bound kernels (large enough that a launch "
+                                                              "lasts several times the host's launch path)")
     ap.add_argument("--peaks", default="")
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
@@ -167,12 +174,13 @@ def main(argv=None) -> None:
     tm = Timer(dev)
     rows = []
     if "attn" in a.what:
-        bench_attention(tm, rows, [(D, Hq, Hkv, T) for T in a.T for D, Hq, Hkv in ((64, 32, 8), (128, 16, 4))], tfl)
+        bench_attention(tm, rows, [(D, Hq, Hkv, T) for T in a.T for D, Hq, Hkv in ((64, 32, 8), (128, 16, 4)) if D in a.head_dims], tfl,
+                        a.attn_pass)
     if "gemm" in a.what:
         # 8192^3 and the Llama-1B layer shapes at 16384 local tokens: QKV / O projection, gate_up, down
         bench_gemm(tm, rows, [(8192, 8192, 8192), (16384, 3072, 2048), (16384, 2048, 2048), (16384, 16384, 2048), (16384, 2048, 8192)], tfl)
     if "membound" in a.what:
-        bench_membound(tm, rows, 32768, 2048, hbm)
+        bench_membound(tm, rows, a.rows, 2048, hbm)
     from context_parallelism_b200 import _native as nv
     nv.status_for(dev).check("kernel_bench")
     hdr = {"peaks": src, "hbm_gbs": hbm, "bf16_tflops": tfl}

@@ -511,12 +511,13 @@ class _FusedRingFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do):
-        q, out, lse, pos32, slot_t = ctx.saved_tensors[:5]
+        saved = ctx.saved_tensors          # read exactly once: under activation recomputation a second read is an error
+        q, out, lse, pos32, slot_t = saved[:5]
         fc, rb, scale = ctx.fc, ctx.rb, ctx.scale
         slot = int(slot_t.item())
         do = do.contiguous()
         if fc.share_ring_slots:
-            rb, slot = ring_fwd_publish(fc, ctx.saved_tensors[5], ctx.saved_tensors[6])
+            rb, slot = ring_fwd_publish(fc, saved[5], saved[6])
         ring_bwd_prepare(fc, rb)
         fc.barrier(fc.g_ring)                  # every accumulator is zero, every published K/V is still in place
         dq = ring_bwd_compute(fc, rb, slot, q, out, lse, do, pos32, scale)

@@ -107,7 +107,10 @@ def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0) ->
     import datetime
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    # without a launcher-provided LOCAL_RANK the device is rank % NO_GPUS_PER_NODE, as in the reference
+    # (process_group/device_mesh.cpp:126-133)
+    gpn = int(os.environ.get("NO_GPUS_PER_NODE", "0") or 0) or (torch.cuda.device_count() if torch.cuda.is_available() else 1) or 1
+    local = int(os.environ["LOCAL_RANK"]) if "LOCAL_RANK" in os.environ else rank % gpn
     if world > 1 and not dist.is_initialized():
         if backend is None:
             backend = "nccl" if torch.cuda.is_available() else "gloo"

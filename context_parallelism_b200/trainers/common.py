@@ -69,6 +69,13 @@ def train(cfg: Config, eng: TrainEngine, impl: str, csv_header: str,
         with open(os.path.join(cfg.log_dir, f"{cfg.ckpt_prefix}_run{run}_config.txt"), "w") as f:
             f.write(cfg.describe() + "\n")
     timers = M.PhaseTimers(dev)
+    alloc_csv = None
+    if cfg.alloc_csv and rank == 0:
+        # CP_ALLOC_CSV: one row of caching-allocator statistics per step (gpt2_cp_test.cpp:1802)
+        os.makedirs(os.path.dirname(os.path.abspath(cfg.alloc_csv)), exist_ok=True)
+        alloc_csv = open(cfg.alloc_csv, "a" if resuming else "w")
+        if not resuming:
+            alloc_csv.write("step,allocated_mb,reserved_mb,peak_allocated_mb,peak_reserved_mb,num_alloc_retries,driver_used_mb\n")
     tokens_per_step = cfg.B * cfg.T * dp_size * accum
     val_loss = float("nan")
     M.log(f"[{impl}] world={cfg.world_size} dp={dp_size} cp={cfg.cp_size} mode={cfg.attn_mode} rotator={cfg.rotator} "
@@ -111,6 +118,19 @@ def train(cfg: Config, eng: TrainEngine, impl: str, csv_header: str,
         csv.row(step=step, loss=loss, val_loss=val_loss, lr=lr, grad_norm=float(norm), dt_ms=dt_ms, tok_per_sec=tok_s,
                 timer_data=ph.get("timer_data", 0.0), timer_fwd=ph.get("timer_fwd_bwd", 0.0), timer_optim=ph.get("timer_optim", 0.0),
                 mem_gpu_mb=mem)
+        if alloc_csv is not None:
+            st = torch.cuda.memory_stats(dev) if dev.type == "cuda" else {}
+            mb = lambda k: st.get(k, 0) / 2 ** 20          # noqa: E731
+            alloc_csv.write(f"{step},{mb('allocated_bytes.all.current'):.1f},{mb('reserved_bytes.all.current'):.1f},"
+                            f"{mb('allocated_bytes.all.peak'):.1f},{mb('reserved_bytes.all.peak'):.1f},{st.get('num_alloc_retries', 0)},{mem:.0f}\n")
+            alloc_csv.flush()
+        if cfg.debug.dump_fwd and step == start_step:
+            # DUMP_FWD: the first step's forward result for cross-implementation parity (loss and final hidden state)
+            with torch.no_grad():
+                idx, _, pos = eng.shard_batch(x, None)
+                hdn = eng.model.hidden(idx, pos)
+            from ..utils.debug import DebugTools
+            DebugTools(cfg, rank).dump(True, "fwd", step, hidden=hdn, loss=torch.tensor([loss]), positions=pos.float())
         last_loss = loss
         if use_ckpt and ((step + 1) % cfg.ckpt_freq == 0 or step + 1 == max_steps):
             mgr.save(run, step + 1, eng.model, eng.flat, eng.opt, loss)
@@ -120,5 +140,7 @@ def train(cfg: Config, eng: TrainEngine, impl: str, csv_header: str,
         if rank == 0:
             M.write_mem_snapshot(path, cfg, impl, cfg.rotator, dev, {"final_loss": last_loss})
         M.log(f"[mem-probe] snapshot {path}")
+    if alloc_csv is not None:
+        alloc_csv.close()
     train_ld.close()
     val_ld.close()

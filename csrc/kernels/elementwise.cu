@@ -334,43 +334,21 @@ __global__ void embedding_bwd_kernel(const int64_t* __restrict__ idx, const int6
 }
 
 // ============================================================================ QK-norm + RoPE
-// Packed QKV [rows = B*T, (Hq + 2*Hkv) * D] bf16.  For every q and k head vector: optional RMS-norm with
-// gain gamma_q / gamma_k, then NeoX rotation by cache row pos[t].  v is copied.  One warp handles one
-// (row, head) vector: D/2 <= 64 -> lane owns elements (2*lane, 2*lane+1) of each half ... we use
-// lane -> pair index i and i+32 (D=128) layout: element a = x[i], b = x[i+half].
+// Packed QKV [rows = B*T, (Hq + 2*Hkv) * D] bf16.  For every q and k head vector: optional RMS-norm with gain
+// gamma_q / gamma_k, then NeoX rotation by cache row pos[t] (element e pairs with e + D/2); v is copied.
+// A head vector is handled by D/8 adjacent lanes, each holding 8 consecutive elements (one 16-byte access), so a warp
+// covers 4 (D = 64) or 2 (D = 128) vectors at a time; the lanes of the first half of the vector exchange values with
+// the lanes of the second half by shuffle, and the sum of squares is reduced inside the lane group.
 // Output: out (same packed shape, may alias in).  rstd (optional) [rows, Hq+Hkv] fp32.
-// dst_* describe the destination addressing so the same kernel can scatter straight into a peer's
-// landing zone for the Ulysses all-to-all (see ulysses.cu); here dst is a plain packed buffer.
 template <int D>
-__device__ __forceinline__ void norm_rope_vec(float (&a)[D / 64], float (&b)[D / 64], const float* gamma, float eps,
-                                              const float* cache_row, int lane, float* rstd_out) {
-  constexpr int PER = D / 64;     // pairs per lane
-  constexpr int half = D / 2;
-  if (gamma) {
-    float ss = 0.f;
+__device__ __forceinline__ float group_sum(float v) {
 #pragma unroll
-    for (int i = 0; i < PER; ++i) ss += a[i] * a[i] + b[i] * b[i];
-    ss = warp_sum(ss);
-    float rstd = rsqrtf(ss / D + eps);
-    if (rstd_out && lane == 0) *rstd_out = rstd;
-#pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      const int e = lane + i * 32;
-      // round through bf16 between norm and rotation exactly as a two-kernel pipeline would not; keep fp32
-      a[i] = a[i] * rstd * gamma[e];
-      b[i] = b[i] * rstd * gamma[e + half];
-    }
-  }
-  if (cache_row) {
-#pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      const int e = lane + i * 32;
-      const float c = cache_row[e], s = cache_row[e + half];
-      const float x = a[i], y = b[i];
-      a[i] = x * c - y * s;
-      b[i] = x * s + y * c;
-    }
-  }
+  for (int o = D / 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ void load8_f32(const float* p, float (&v)[8]) {
+  const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
 template <int D>
@@ -379,36 +357,54 @@ __global__ void qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, __
                                         const float* __restrict__ cache, const int64_t* __restrict__ pos,
                                         float* __restrict__ rstd, size_t rows, int T, int Hq, int Hkv, float eps,
                                         int cache_len, int* status) {
-  constexpr int PER = D / 64, half = D / 2;
+  constexpr int GL = D / 8, VPW = 32 / GL, half = D / 2;
   const int H = Hq + 2 * Hkv;
   const int lane = threadIdx.x & 31;
+  const int gl = lane % GL;                         // lane inside its vector's group
+  const bool second = gl >= GL / 2;                 // this lane holds elements of the second half
+  const int e0 = gl * 8;                            // first element this lane holds
+  const int eh = (gl % (GL / 2)) * 8;               // the same position inside a half (index into cos / sin)
   const size_t nvec = rows * H;
-  for (size_t w = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); w < nvec; w += (size_t)gridDim.x * (blockDim.x >> 5)) {
-    const size_t row = w / H;
-    const int h = (int)(w % H);
-    const __nv_bfloat16* src = in + row * (size_t)H * D + (size_t)h * D;
-    __nv_bfloat16* dst = out + row * (size_t)H * D + (size_t)h * D;
-    float a[PER], b[PER];
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t w0 = (blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5)) * VPW; w0 < nvec; w0 += warps * VPW) {
+    const size_t w = w0 + lane / GL;
+    const bool live = w < nvec;
+    const size_t row = live ? w / H : 0;
+    const int h = live ? (int)(w % H) : H - 1;
+    float x[8];
+    if (live) { uint4 u = *(const uint4*)(in + w * D + e0); unpack8(u, x); }
+    else {
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      a[i] = __bfloat162float(src[lane + i * 32]);
-      b[i] = __bfloat162float(src[lane + i * 32 + half]);
+      for (int i = 0; i < 8; ++i) x[i] = 0.f;
     }
-    if (h < Hq + Hkv) {
-      const float* cr = nullptr;
-      if (cache) {
-        const int64_t p = pos[row % T];
-        if (p >= 0 && p < cache_len) cr = cache + (size_t)p * D;
-        else report(status, ST_BAD_INDEX, 400, (int)p);
-      }
-      float* rs = rstd ? rstd + row * (size_t)(Hq + Hkv) + h : nullptr;
-      norm_rope_vec<D>(a, b, h < Hq ? gq : gk, eps, cr, lane, rs);
-    }
+    const bool rot = h < Hq + Hkv;                  // uniform inside a lane group
+    const float* gamma = h < Hq ? gq : gk;
+    float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      dst[lane + i * 32] = __float2bfloat16(a[i]);
-      dst[lane + i * 32 + half] = __float2bfloat16(b[i]);
+    for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+    ss = group_sum<D>(ss);
+    if (rot && gamma) {
+      const float r = rsqrtf(ss / D + eps);
+      if (rstd && gl == 0 && live) rstd[row * (size_t)(Hq + Hkv) + h] = r;
+      float g[8];
+      load8_f32(gamma + e0, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = x[i] * r * g[i];
     }
+    const float* cr = nullptr;
+    if (rot && cache && live) {
+      const int64_t p = pos[row % T];
+      if (p >= 0 && p < cache_len) cr = cache + (size_t)p * D;
+      else report(status, ST_BAD_INDEX, 400, (int)p);
+    }
+    float c[8], sn[8];
+    if (cr) { load8_f32(cr + eh, c); load8_f32(cr + half + eh, sn); }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[i], GL / 2);      // the paired element of the other half
+      if (cr) x[i] = second ? other * sn[i] + x[i] * c[i] : x[i] * c[i] - other * sn[i];
+    }
+    if (live) *(uint4*)(out + w * D + e0) = pack8(x);
   }
 }
 
@@ -421,83 +417,79 @@ __global__ void qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ in, co
                                         const float* __restrict__ gk, const float* __restrict__ cache,
                                         const int64_t* __restrict__ pos, float* __restrict__ dgq, float* __restrict__ dgk,
                                         size_t rows, int T, int Hq, int Hkv, float eps, int cache_len) {
-  constexpr int PER = D / 64, half = D / 2;
+  constexpr int GL = D / 8, VPW = 32 / GL, half = D / 2;
   __shared__ float sg[2][D];
   for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&sg[0][0])[i] = 0.f;
   __syncthreads();
   const int H = Hq + 2 * Hkv;
   const int lane = threadIdx.x & 31;
+  const int gl = lane % GL;
+  const bool second = gl >= GL / 2;
+  const int e0 = gl * 8, eh = (gl % (GL / 2)) * 8;
   const size_t nvec = rows * H;
-  float accq_a[PER], accq_b[PER], acck_a[PER], acck_b[PER];
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  float accq[8], acck[8];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) { accq_a[i] = accq_b[i] = acck_a[i] = acck_b[i] = 0.f; }
-  for (size_t w = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); w < nvec; w += (size_t)gridDim.x * (blockDim.x >> 5)) {
-    const size_t row = w / H;
-    const int h = (int)(w % H);
-    const size_t off = row * (size_t)H * D + (size_t)h * D;
-    float da[PER], dbv[PER];
+  for (int i = 0; i < 8; ++i) accq[i] = acck[i] = 0.f;
+  for (size_t w0 = (blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5)) * VPW; w0 < nvec; w0 += warps * VPW) {
+    const size_t w = w0 + lane / GL;
+    const bool live = w < nvec;
+    const size_t row = live ? w / H : 0;
+    const int h = live ? (int)(w % H) : H - 1;
+    float d[8];
+    if (live) { uint4 u = *(const uint4*)(dout + w * D + e0); unpack8(u, d); }
+    else {
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      da[i] = __bfloat162float(dout[off + lane + i * 32]);
-      dbv[i] = __bfloat162float(dout[off + lane + i * 32 + half]);
+      for (int i = 0; i < 8; ++i) d[i] = 0.f;
     }
-    if (h < Hq + Hkv) {
-      const float* g = h < Hq ? gq : gk;
-      if (cache) {
-        const int64_t p = pos[row % T];
-        if (p >= 0 && p < cache_len) {
-          const float* cr = cache + (size_t)p * D;
+    const bool rot = h < Hq + Hkv;
+    const float* g = h < Hq ? gq : gk;
+    const float* cr = nullptr;
+    if (rot && cache && live) {
+      const int64_t p = pos[row % T];
+      if (p >= 0 && p < cache_len) cr = cache + (size_t)p * D;
+    }
+    float c[8], sn[8];
+    if (cr) { load8_f32(cr + eh, c); load8_f32(cr + half + eh, sn); }
 #pragma unroll
-          for (int i = 0; i < PER; ++i) {
-            const int e = lane + i * 32;
-            const float c = cr[e], s = cr[e + half];
-            const float x = da[i], y = dbv[i];
-            da[i] = x * c + y * s;          // transpose of the rotation
-            dbv[i] = -x * s + y * c;
-          }
-        }
-      }
-      if (g) {
-        float xa[PER], xb[PER];
-        float ss = 0.f;
+    for (int i = 0; i < 8; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, d[i], GL / 2);
+      if (cr) d[i] = second ? d[i] * c[i] - other * sn[i] : d[i] * c[i] + other * sn[i];     // transpose of the rotation
+    }
+    float xh[8];
+    if (live && rot && g) { uint4 u = *(const uint4*)(in + w * D + e0); unpack8(u, xh); }
+    else {
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-          xa[i] = __bfloat162float(in[off + lane + i * 32]);
-          xb[i] = __bfloat162float(in[off + lane + i * 32 + half]);
-          ss += xa[i] * xa[i] + xb[i] * xb[i];
-        }
-        ss = warp_sum(ss);
-        const float rstd = rsqrtf(ss / D + eps);
-        float dot = 0.f;
+      for (int i = 0; i < 8; ++i) xh[i] = 0.f;
+    }
+    float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-          const int e = lane + i * 32;
-          xa[i] *= rstd; xb[i] *= rstd;
-          if (h < Hq) { accq_a[i] += da[i] * xa[i]; accq_b[i] += dbv[i] * xb[i]; }
-          else        { acck_a[i] += da[i] * xa[i]; acck_b[i] += dbv[i] * xb[i]; }
-          da[i] *= g[e]; dbv[i] *= g[e + half];
-          dot += da[i] * xa[i] + dbv[i] * xb[i];
-        }
-        dot = warp_sum(dot) / D;
+    for (int i = 0; i < 8; ++i) ss += xh[i] * xh[i];
+    ss = group_sum<D>(ss);
+    // every shuffle below is executed by the whole warp: lane groups of one warp may hold different kinds of heads
+    const bool normed = rot && g != nullptr;
+    const float r = rsqrtf(ss / D + eps);
+    float dot = 0.f;
+    if (normed) {
+      float gv[8];
+      load8_f32(g + e0, gv);
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-          da[i] = rstd * (da[i] - xa[i] * dot);
-          dbv[i] = rstd * (dbv[i] - xb[i] * dot);
-        }
+      for (int i = 0; i < 8; ++i) {
+        xh[i] *= r;
+        if (h < Hq) accq[i] += d[i] * xh[i]; else acck[i] += d[i] * xh[i];
+        d[i] *= gv[i];
+        dot += d[i] * xh[i];
       }
     }
+    dot = group_sum<D>(dot) / D;
+    if (normed) {
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      din[off + lane + i * 32] = __float2bfloat16(da[i]);
-      din[off + lane + i * 32 + half] = __float2bfloat16(dbv[i]);
+      for (int i = 0; i < 8; ++i) d[i] = r * (d[i] - xh[i] * dot);
     }
+    if (live) *(uint4*)(din + w * D + e0) = pack8(d);
   }
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int e = lane + i * 32;
-    atomicAdd(&sg[0][e], accq_a[i]); atomicAdd(&sg[0][e + half], accq_b[i]);
-    atomicAdd(&sg[1][e], acck_a[i]); atomicAdd(&sg[1][e + half], acck_b[i]);
-  }
+  for (int i = 0; i < 8; ++i) { atomicAdd(&sg[0][e0 + i], accq[i]); atomicAdd(&sg[1][e0 + i], acck[i]); }
   __syncthreads();
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     if (dgq) atomicAdd(&dgq[i], sg[0][i]);
@@ -820,7 +812,7 @@ extern "C" int cpb_qk_norm_rope_fwd(const void* in, void* out, const float* gq, 
                                     const int64_t* pos, float* rstd, long rows, int T, int Hq, int Hkv, int D,
                                     float eps, int cache_len, int* status, cudaStream_t stream) {
   if (rows <= 0) return CPB_OK;
-  const int grid = grid_for((size_t)rows * (Hq + 2 * Hkv), 8);
+  const int grid = grid_for((size_t)rows * (Hq + 2 * Hkv) / (256 / D) + 1, 8);      // a warp covers 256/D vectors per pass
   if (D == 64) qk_norm_rope_fwd_kernel<64><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, gq, gk, cache, pos, rstd, (size_t)rows, T, Hq, Hkv, eps, cache_len, status);
   else if (D == 128) qk_norm_rope_fwd_kernel<128><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, gq, gk, cache, pos, rstd, (size_t)rows, T, Hq, Hkv, eps, cache_len, status);
   else return set_error(CPB_ERR_ARG, "qk_norm_rope: head_dim %d not in {64,128}", D);
@@ -830,7 +822,7 @@ extern "C" int cpb_qk_norm_rope_bwd(const void* in, const void* dout, void* din,
                                     const float* cache, const int64_t* pos, float* dgq, float* dgk, long rows, int T,
                                     int Hq, int Hkv, int D, float eps, int cache_len, cudaStream_t stream) {
   if (rows <= 0) return CPB_OK;
-  const int grid = grid_for((size_t)rows * (Hq + 2 * Hkv), 8, 4);
+  const int grid = grid_for((size_t)rows * (Hq + 2 * Hkv) / (256 / D) + 1, 8, 4);
   if (D == 64) qk_norm_rope_bwd_kernel<64><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, (const __nv_bfloat16*)dout, (__nv_bfloat16*)din, gq, gk, cache, pos, dgq, dgk, (size_t)rows, T, Hq, Hkv, eps, cache_len);
   else if (D == 128) qk_norm_rope_bwd_kernel<128><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, (const __nv_bfloat16*)dout, (__nv_bfloat16*)din, gq, gk, cache, pos, dgq, dgk, (size_t)rows, T, Hq, Hkv, eps, cache_len);
   else return set_error(CPB_ERR_ARG, "qk_norm_rope: head_dim %d not in {64,128}", D);

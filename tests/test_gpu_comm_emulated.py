@@ -49,13 +49,14 @@ def dense_reference(q, k, v, do, scale):
 
 
 # ----------------------------------------------------------------------------------------------------- ring
-@pytest.mark.parametrize("n,hq,hkv,dkv_mode,lb", [(2, 4, 2, "route", True), (4, 4, 2, "route", True), (4, 4, 1, "pull", True),
-                                                  (2, 2, 2, "pull", True), (4, 4, 2, "route", False), (2, 4, 4, "pull", False)])
-def test_fused_ring_emulated(n, hq, hkv, dkv_mode, lb):
+@pytest.mark.parametrize("n,hq,hkv,dkv_mode,lb,D", [(2, 4, 2, "route", True, 64), (4, 4, 2, "route", True, 64), (4, 4, 1, "pull", True, 64),
+                                                    (2, 2, 2, "pull", True, 64), (4, 4, 2, "route", False, 64), (2, 4, 4, "pull", False, 64),
+                                                    (2, 4, 2, "route", True, 128), (4, 2, 1, "pull", True, 128)])
+def test_fused_ring_emulated(n, hq, hkv, dkv_mode, lb, D):
     from context_parallelism_b200.parallel import fused as F
     from context_parallelism_b200.parallel import shard
     torch.manual_seed(n * 10 + hq)
-    B, T, D = 2, 256 * n, 64
+    B, T = 2, 256 * n
     Tl = T // n
     scale = D ** -0.5
     cfg, fcs = make_comms(n, "ring", dkv_mode=dkv_mode, load_balance_ring=lb)

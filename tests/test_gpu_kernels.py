@@ -157,7 +157,7 @@ def test_flash_fwd(D, B, Tq, Tk, Hq, Hkv, causal):
     out, lse = A.flash_fwd(q, k, v, scale, causal)
     check_status()
     want, wlse = R.attention_dense(q.float(), k.float(), v.float(), scale, causal=causal)
-    assert_close(out.float(), want, cos=0.999, rel=3e-2, name="out")
+    assert_close(out.float(), want, cos=0.9995, rel=3e-2, name="out")
     assert_close(lse, wlse, cos=0.99999, rel=1e-3, name="lse")
 
 
@@ -175,7 +175,7 @@ def test_flash_fwd_positions_packed():
     out, lse = A.flash_fwd(q, k, v, 0.125, True, q_pos=pos.int())
     check_status()
     want, wlse = R.attention_dense(q.float(), k.float(), v.float(), 0.125, q_pos=pos, causal=True)
-    assert_close(out.float(), want, cos=0.999, rel=3e-2, name="out")
+    assert_close(out.float(), want, cos=0.9995, rel=3e-2, name="out")
     assert_close(lse, wlse, cos=0.99999, rel=1e-3, name="lse")
 
 
@@ -196,9 +196,9 @@ def test_flash_bwd(D, B, Tq, Tk, Hq, Hkv, causal):
     check_status()
     want, wlse = R.attention_dense(q.float(), k.float(), v.float(), scale, causal=causal)
     wdq, wdk, wdv = R.attention_dense_bwd(q.float(), k.float(), v.float(), want, wlse, do.float(), scale, causal=causal)
-    assert_close(dv.float(), wdv, cos=0.995, rel=5e-2, name="dv")
-    assert_close(dk.float(), wdk, cos=0.995, rel=5e-2, name="dk")
-    assert_close(dq.float(), wdq, cos=0.995, rel=5e-2, name="dq")
+    assert_close(dv.float(), wdv, cos=0.998, rel=5e-2, name="dv")
+    assert_close(dk.float(), wdk, cos=0.998, rel=5e-2, name="dk")
+    assert_close(dq.float(), wdq, cos=0.998, rel=5e-2, name="dq")
 
 
 @pytest.mark.parametrize("B,Tq,Tk,Hq,Hkv,causal", [(1, 512, 512, 4, 1, True), (2, 300, 712, 2, 2, False), (1, 2048, 2048, 8, 2, True)])
@@ -246,9 +246,9 @@ def test_flash_autograd_positions():
     Q, K, V = (t.detach().float().cpu().requires_grad_() for t in (q, k, v))
     want, _ = A.flash_attention(Q, K, V, None, True, pos.cpu())
     want.backward(do.float().cpu())
-    assert_close(out.float().cpu(), want, cos=0.999, name="out")
+    assert_close(out.float().cpu(), want, cos=0.9995, name="out")
     for a, b_, n in ((q, Q, "dq"), (k, K, "dk"), (v, V, "dv")):
-        assert_close(a.grad.float().cpu(), b_.grad, cos=0.995, name=n)
+        assert_close(a.grad.float().cpu(), b_.grad, cos=0.998, name=n)
 
 
 @pytest.mark.parametrize("D,Hq,Hkv", [(64, 4, 2), (128, 2, 1), (32, 4, 4)])

@@ -116,3 +116,29 @@ def test_gpt2_trainer_named_init_and_generation(tmp_path):
     out2 = run("context_parallelism_b200.trainers.gpt2_cp", dict(env, LOAD_INIT_NAMED=env["SAVE_INIT_NAMED"], CP_SEED="999", SAVE_INIT_NAMED=""), nproc=2)
     first2 = [l for l in out2.splitlines() if l.startswith("step     0")][0]
     assert first.split("|")[1] == first2.split("|")[1]
+
+
+def test_debug_knobs_take_effect_or_are_refused(tmp_path):
+    """Every diagnostic name of the reference either does something observable or is refused at start-up; none is
+    parsed and ignored."""
+    env = {"CP_CKPT": "0", "CP_MAX_STEPS": "2", "CP_LOG_DIR": tmp_path, "CP_ATTN_MODE": "ring", "CP_ROTATOR": "p2p", "CP_VAL_FREQ": "0",
+           "CP_ALLOC_CSV": tmp_path / "alloc.csv", "DUMP_FWD": "1", "CP_DEBUG_SHAPES": "1", "CP_DRAIN_AT": "2", "DUMP_CP_OUT": "1",
+           "DUMP_CP_STEPS": "1", "DUMP_CP_MERGE": "1", "CP_RING_BLOCKING": "1", "CP_FWD_SYNC_RETURN": "1"}
+    out = run("context_parallelism_b200.trainers.llama_cp", env, nproc=2)
+    assert "[CP_DEBUG_SHAPES] rank 0 ring forward" in out and "step     1" in out
+    rows = list(csv.reader(open(tmp_path / "alloc.csv")))
+    assert rows[0][0] == "step" and [r[0] for r in rows[1:]] == ["0", "1"]
+    names = sorted(f.name for f in tmp_path.glob("dump_*.pt"))
+    assert "dump_fwd_rank0_call0.pt" in names and "dump_cp_out_rank1_call0.pt" in names
+    assert any(n.startswith("dump_cp_step1_") for n in names) and any(n.startswith("dump_cp_merge1_") for n in names)
+    import torch
+    d = torch.load(tmp_path / "dump_cp_out_rank0_call0.pt")
+    assert set(d) == {"out", "lse"} and d["out"].dim() == 4
+    from context_parallelism_b200.config import Config
+    for bad in ({"CP_NVLS": "1"}, {"USE_PER_STEP_LSE": "1"}, {"CP_DKV_MODE": "sideways"}, {"CP_RECOMPUTE": "most"},
+                {"CP_RING_BF16": "0", "CP_DTYPE": "bf16"}):
+        with pytest.raises(ValueError):
+            Config.from_env("llama", 1, env=bad).validate()
+    # the reference's spelling of the dK/dV modes is accepted
+    assert Config.from_env("llama", 1, env={"CP_DKV_MODE": "red"}).dkv_mode == "route"
+    assert Config.from_env("llama", 1, env={"CP_DKV_MODE": "pull"}).dkv_mode == "pull"
