@@ -165,8 +165,8 @@ class FusedComm:
     @staticmethod
     def create(cfg, ctx, device) -> Optional["FusedComm"]:
         world = dist.get_world_size()
-        if world > torch.cuda.device_count():
-            return None            # more ranks than local GPUs: not a single-node job, CUDA IPC does not apply
+        if world > min(torch.cuda.device_count(), max(1, cfg.gpus_per_node)):
+            return None            # more ranks than GPUs of one node (NO_GPUS_PER_NODE): not a single-node job, CUDA IPC does not apply
         heap = SymmetricHeap(None, FusedComm.estimate_bytes(cfg, ctx, world), device)
         mesh = ctx.mesh
         ring = uly = None

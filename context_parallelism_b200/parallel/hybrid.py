@@ -24,6 +24,13 @@ def hybrid_attention(q, k, v, ctx, attn, fused: bool):
     fused_uly = (fused and U > 1 and os.environ.get("CP_FUSED_HYBRID_ULYSSES", "0") == "1"
                  and getattr(ctx.fused, "g_uly", None) is not None and q.dtype == torch.bfloat16)
     ub = None
+    dbg = getattr(attn, "dbg", None)
+    if dbg is not None and dbg.d.selfcheck and U > 1 and not fused_uly:
+        # CP_SELFCHECK in hybrid mode: the sequence<->head exchange must be an exact round trip
+        # (context_parallel/ContextParallel.h:1307-1327)
+        with torch.no_grad():
+            back = head_to_seq(seq_to_head(q.detach().contiguous(), ctx.ulysses_group), ctx.ulysses_group)
+        dbg.selfcheck("hybrid combine/partition round trip", dbg.next_call("hybrid"), {"q": q.detach()}, lambda: {"q": back})
     if fused_uly:
         from .fused import fused_head_to_seq, fused_seq_to_head
         q, k, v, ub = fused_seq_to_head(ctx.fused, q, k, v)
