@@ -44,7 +44,10 @@ namespace cpb {
 
 constexpr int B64_T = 128;
 constexpr int B64_D = 64;
-constexpr int B64_THREADS = 448;
+// Warps: 0 = TMA loader, 1 = MMA issuer, then 4*NG softmax-gradient warps (NG column groups of 128/NG queries; a warp
+// can only touch the 32 tensor-memory lanes of its quarter, so every group has four warps), then 4 dQ drain warps.
+constexpr int b64_threads(int ng) { return 64 + 128 * ng + 128; }
+constexpr int B64_NG = 4;          // column groups of the softmax-gradient warps (2: 64 queries per thread, 4: 32)
 constexpr int B64_POLY = 0;        // share (of 8) of the exponentials computed on the FMA pipe: measured neutral (846 to 855 TFLOP/s for 0..4), kept off
 
 static __device__ long long g_bwd64_prof[16 + 32 * 8];
@@ -112,13 +115,15 @@ __device__ __forceinline__ void red_add_v4_64(float* addr, float a, float b, flo
 
 // POLY: of the 8 column pairs of every 16-column group of an unmasked tile, the last POLY take their exponentials from
 // exp2_poly_f32x2 (FMA pipe) and the others from ex2.approx (special-function unit).
-template <int POLY>
-__global__ void __launch_bounds__(B64_THREADS, 1)
+template <int POLY, int NG>
+__global__ void __launch_bounds__(b64_threads(NG), 1)
 flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const __grid_constant__ CUtensorMap tmDQ, Bwd64Params p) {
   using L = Bwd64Smem;
   constexpr int D = B64_D;
+  constexpr int CW = B64_T / NG;            // query columns per softmax-gradient thread
+  constexpr int NCH = CW / 16;              // 16-column groups per thread
   constexpr uint32_t ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 320, DQ_COL = 384, PT_COL = 448;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -147,8 +152,8 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < NST; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
-    mbar_init(s_ready, 1); mbar_init(s_consumed, 8); mbar_init(dp_ready, 1);
-    mbar_init(p_full, 8); mbar_init(dq_full, 1); mbar_init(dq_empty, 4); mbar_init(acc_done, 1);
+    mbar_init(s_ready, 1); mbar_init(s_consumed, 4 * NG); mbar_init(dp_ready, 1);
+    mbar_init(p_full, 4 * NG); mbar_init(dq_full, 1); mbar_init(dq_empty, 4); mbar_init(acc_done, 1);
     *abort_flag = 0;
     *qt_start_s = num_q_tiles;
     fence_mbar_init();
@@ -272,7 +277,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         umma_ts_p(leader, t_dk, t_dp, sdesc_at(qn, 0), idesc_acc, i != 0);            // dK += dS^T Q  (frees the dS^T alias)
 #pragma unroll
         for (int k = 1; k < B64_T / 16; ++k)
-          umma_ts_cp<true>(leader, t_dk, t_dp + (k >> 2) * 64 + (k & 3) * 8, sdesc_at(qn, k * 2048), idesc_acc);
+          umma_ts_cp<true>(leader, t_dk, t_dp + ((16 * k) / CW) * CW + (((16 * k) % CW) / 16) * 8, sdesc_at(qn, k * 2048), idesc_acc);
         B64_STAMP(wr_prof, i, 4);
         if (i + 1 < n_it) issue_dp((i + 1) % NST);                                     // dP'(i+1): early, off the warps' critical path
         B64_STAMP(wr_prof, i, 5);
@@ -297,17 +302,21 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (wr_prof) p.prof[15] = n_it;
 #endif
     }
-  } else if (warp >= 2 && warp < 10) {
-    // ------------------------------------------------------------------ softmax-gradient warps (thread = key row, 64 queries)
+  } else if (warp >= 2 && warp < 2 + 4 * NG) {
+    // ------------------------------------------------------------------ softmax-gradient warps (thread = key row, CW queries)
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;                   // which 64 query columns of the tile this thread owns
-    const int cbase = half * 64;
+    const int grp = (warp - 2) >> 2;                    // which CW query columns of the tile this thread owns
+    const int cbase = grp * CW;
     const int r = quarter * 32 + lane;                  // key row inside the tile
     const int kidx = k0 + r;
     const bool k_valid = kidx < p.Tk;
     const int kpos = p.k_off + kidx;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    uint8_t* ds_row = smem + L::DS_OFF + half * (B64_T * 128) + r * 128;
+    // dS^T in shared memory: two [128 keys x 64 queries] halves, 128-byte swizzled rows; this thread's queries start at
+    // 16-byte chunk `chunk0` of its row in half cbase / 64
+    uint8_t* ds_row = smem + L::DS_OFF + (cbase / 64) * (B64_T * 128) + r * 128;
+    constexpr int DS_CHUNKS = CW / 8;
+    const int chunk0 = (cbase % 64) / 8;
     bool alive = true;
     const bool wprof = B64_PROF_ON(p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64);
     // first query position of a tile decides whether it needs masking; read one tile ahead, straight from global memory
@@ -327,17 +336,17 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       B64_STAMP(wprof, i, 9);
       const int* qpos = (const int*)(smem + L::QPOS_OFF + st * 512);
-      uint32_t sv[4][16];
+      uint32_t sv[NCH][16];
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) tmem_ld16(t_lane + ST_COL + cbase + 16 * ch, sv[ch]);
+      for (int ch = 0; ch < NCH; ++ch) tmem_ld16(t_lane + ST_COL + cbase + 16 * ch, sv[ch]);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive_warp(s_consumed);                         // the next score tile may overwrite S'^T
-      uint32_t pk[32];                                  // P^T of this thread's 64 queries, bf16 pairs
+      uint32_t pk[CW / 2];                              // P^T of this thread's queries, bf16 pairs
       if (!need_mask) {
         const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2);
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
+        for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
             if ((j >> 1) >= 8 - POLY) {                 // resolved at compile time (the loops are unrolled)
@@ -350,7 +359,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
       } else {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
+        for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
             const int c = cbase + ch * 16 + j;
@@ -367,20 +376,20 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       B64_STAMP(wprof, i, 12);
       // dS^T = P^T o dP'^T with the bf16-rounded P (the value dV is computed from), kept packed in registers
-      uint32_t dsk[32];
+      uint32_t dsk[CW / 2];
       {
         uint32_t dpv[2][16];
         tmem_ld16(t_lane + DPT_COL + cbase, dpv[0]);
         tmem_wait_ld();
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          if (ch < 3) tmem_ld16(t_lane + DPT_COL + cbase + 16 * (ch + 1), dpv[(ch + 1) & 1]);
+        for (int ch = 0; ch < NCH; ++ch) {
+          if (ch < NCH - 1) tmem_ld16(t_lane + DPT_COL + cbase + 16 * (ch + 1), dpv[(ch + 1) & 1]);
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
             const uint32_t pp = pk[ch * 8 + (j >> 1)];
             dsk[ch * 8 + (j >> 1)] = pack_bf16(bf16_lo(pp) * __uint_as_float(dpv[ch & 1][j]), bf16_hi(pp) * __uint_as_float(dpv[ch & 1][j + 1]));
           }
-          if (ch < 3) tmem_wait_ld();
+          if (ch < NCH - 1) tmem_wait_ld();
         }
       }
       // dq_full(i-1): dV(i-1) has read the previous P^T and dQ(i-1) the previous dS^T in shared memory
@@ -390,14 +399,20 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!ok4) { alive = false; break; }
         tc_fence_after();
       }
-      // P^T -> its own columns (A operand of dV); dS^T -> the front half of this thread's dP'^T span (A operand of dK: k-step
-      // 4*half+ch at columns half*64 + ch*8) and -> shared memory (row = key, 64 queries per 128-byte swizzled row; M-major A of dQ)
+      // P^T -> its own columns (A operand of dV); dS^T -> the front half of this thread's dP'^T span (A operand of dK: the
+      // k-step of queries 16k.. sits at columns (16k / CW) * CW + ((16k % CW) / 16) * 8) and -> shared memory (row = key,
+      // 64 queries per 128-byte swizzled row; M-major A of dQ)
       B64_STAMP(wprof, i, 14);
-      tmem_st32(t_lane + PT_COL + half * 32, pk);
-      tmem_st32(t_lane + DPT_COL + cbase, dsk);
+      if constexpr (CW == 64) {
+        tmem_st32(t_lane + PT_COL + cbase / 2, pk);
+        tmem_st32(t_lane + DPT_COL + cbase, dsk);
+      } else {
+        tmem_st16(t_lane + PT_COL + cbase / 2, pk);
+        tmem_st16(t_lane + DPT_COL + cbase, dsk);
+      }
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8)
-        *(uint4*)(ds_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(dsk[4 * c8], dsk[4 * c8 + 1], dsk[4 * c8 + 2], dsk[4 * c8 + 3]);
+      for (int c8 = 0; c8 < DS_CHUNKS; ++c8)
+        *(uint4*)(ds_row + (((chunk0 + c8) ^ (r & 7)) << 4)) = make_uint4(dsk[4 * c8], dsk[4 * c8 + 1], dsk[4 * c8 + 2], dsk[4 * c8 + 3]);
       tmem_wait_st();
       fence_proxy_async_smem();
       tc_fence_before();
@@ -406,7 +421,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     // final: dK, dV -> global
     if (n_it == 0) {
-      if (p.dkv_mode == 0 && k_valid && half == 0) {
+      if (p.dkv_mode == 0 && k_valid && grp == 0) {
         __nv_bfloat16* dkr = (__nv_bfloat16*)p.dk + (((size_t)b * p.Tk + kidx) * p.Hkv + hkv) * D;
         __nv_bfloat16* dvr = (__nv_bfloat16*)p.dv + (((size_t)b * p.Tk + kidx) * p.Hkv + hkv) * D;
 #pragma unroll
@@ -418,12 +433,14 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok) {
         tc_fence_after();
         const size_t off = (((size_t)b * p.Tk + (k_valid ? kidx : 0)) * p.Hkv + hkv) * D;
-        const int which = half;                          // first warp group drains dK, second dV
+        const int which = grp >= NG / 2;                 // the first half of the warp groups drains dK, the second dV
+        constexpr int DCOLS = D / (NG / 2);              // accumulator columns per warp group
+        const int c_lo = (grp % (NG / 2)) * DCOLS;
         const uint32_t col = which ? DV_COL : DK_COL;
         void* base = which ? p.dv : p.dk;
         const float osc = which ? 1.f : p.scale;         // dS^T was accumulated without the softmax scale
 #pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
+        for (int c = c_lo; c < c_lo + DCOLS; c += 32) {
           uint32_t v[32];
           tmem_ld32(t_lane + col + c, v);
           tmem_wait_ld();
@@ -462,7 +479,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
   } else {
-    // ------------------------------------------------------------------ dQ drain warps (10..13)
+    // ------------------------------------------------------------------ dQ drain warps (the last four)
     // tensor memory -> registers -> 128B-swizzled fp32 staging -> TMA reduce-add into the global fp32 dQ (rows past the
     // end of the sequence are clipped by the tensor map).  Every warp drains its own 32 query rows through its own
     // staging slice with its own bulk group, so the four warps never wait for one another; the reduce of tile i is read
@@ -473,7 +490,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const bool issuer = (lane == 0);
     if (issuer) tma_prefetch_desc(&tmDQ);
     for (int i = 0; i < n_it; ++i) {
-      const bool dprof = B64_PROF_ON(p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 10 && issuer);
+      const bool dprof = B64_PROF_ON(p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 2 + 4 * NG && issuer);
       const bool dprof_all = B64_PROF_ON(p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && i >= 64 && i < 72);
       bool ok = mbar_wait(dq_full, i & 1, abort_flag, p.status, 1100);
       ok = __all_sync(0xffffffffu, ok);
@@ -610,19 +627,25 @@ extern "C" int cpb_flash_bwd64(const void* q, const void* k, const void* v, cons
     if (cudaGetSymbolAddress(&sym, g_bwd64_prof) == cudaSuccess) { p.prof = (long long*)sym; cudaMemsetAsync(sym, 0, sizeof(long long) * (16 + 32 * 8), stream); }
   }
   dim3 grid((Tk + B64_T - 1) / B64_T, Hkv, B);
-#define CPB_BWD64_LAUNCH(PP)                                                                                            \
+#define CPB_BWD64_LAUNCH(PP, GG)                                                                                        \
   do {                                                                                                                  \
     static bool cfg = false;                                                                                            \
-    if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_bwd64_kernel<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd64Smem::TOTAL)); cfg = true; } \
-    flash_bwd64_kernel<PP><<<grid, B64_THREADS, Bwd64Smem::TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);                   \
+    if (!cfg) { CPB_CUDA_OK(cudaFuncSetAttribute(flash_bwd64_kernel<PP, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd64Smem::TOTAL)); cfg = true; } \
+    flash_bwd64_kernel<PP, GG><<<grid, b64_threads(GG), Bwd64Smem::TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);           \
   } while (0)
-  switch (poly) {
-    case 0: CPB_BWD64_LAUNCH(0); break;
-    case 1: CPB_BWD64_LAUNCH(1); break;
-    case 2: CPB_BWD64_LAUNCH(2); break;
-    case 4: CPB_BWD64_LAUNCH(4); break;
-    case 5: CPB_BWD64_LAUNCH(5); break;
-    default: CPB_BWD64_LAUNCH(3); break;
+  static const int ng = [] { const char* e = getenv("CPB_BWD64_NG"); return e ? atoi(e) : B64_NG; }();
+  if (ng == 2) {
+    switch (poly) {
+      case 3: CPB_BWD64_LAUNCH(3, 2); break;
+      default: CPB_BWD64_LAUNCH(0, 2); break;
+    }
+  } else {
+    switch (poly) {
+      case 2: CPB_BWD64_LAUNCH(2, 4); break;
+      case 3: CPB_BWD64_LAUNCH(3, 4); break;
+      case 4: CPB_BWD64_LAUNCH(4, 4); break;
+      default: CPB_BWD64_LAUNCH(0, 4); break;
+    }
   }
 #undef CPB_BWD64_LAUNCH
   if (p.prof != nullptr) {
