@@ -163,6 +163,7 @@ def main(argv=None) -> None:
     ap.add_argument("--T", type=int, nargs="+", default=[16384])
     ap.add_argument("--head-dims", type=int, nargs="+", default=[64, 128])
     ap.add_argument("--attn-pass", default="both", choices=["both", "fwd", "bwd"])
+    ap.add_argument("--gemm-shape", type=int, nargs=3, default=None, metavar=("M", "N", "K"), help="time this one GEMM shape only")
     ap.add_argument("--rows", type=int, default=131072, help="token rows of the memory-bound kernels (large enough that a launch "
                                                               "lasts several times the host's launch path)")
     ap.add_argument("--peaks", default="")
@@ -178,7 +179,9 @@ def main(argv=None) -> None:
                         a.attn_pass)
     if "gemm" in a.what:
         # 8192^3 and the Llama-1B layer shapes at 16384 local tokens: QKV / O projection, gate_up, down
-        bench_gemm(tm, rows, [(8192, 8192, 8192), (16384, 3072, 2048), (16384, 2048, 2048), (16384, 16384, 2048), (16384, 2048, 8192)], tfl)
+        shapes = [tuple(a.gemm_shape)] if a.gemm_shape else [(8192, 8192, 8192), (16384, 3072, 2048), (16384, 2048, 2048),
+                                                              (16384, 16384, 2048), (16384, 2048, 8192)]
+        bench_gemm(tm, rows, shapes, tfl)
     if "membound" in a.what:
         bench_membound(tm, rows, a.rows, 2048, hbm)
     from context_parallelism_b200 import _native as nv

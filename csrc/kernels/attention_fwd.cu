@@ -313,10 +313,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 16; ++i) if (ch * 16 + i <= kmax) mx = fmaxf(mx, __uint_as_float(sv[ch][i]));
       } else {
+        // four independent chains of eight three-input maxima instead of one chain of thirty-two
+        float m4[4];
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
+        for (int ch = 0; ch < 4; ++ch) {
+          m4[ch] = fmaxf(__uint_as_float(sv[ch][0]), __uint_as_float(sv[ch][1]));
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) mx = fmax3(mx, __uint_as_float(sv[ch][i]), __uint_as_float(sv[ch][i + 1]));
+          for (int i = 2; i < 16; i += 2) m4[ch] = fmax3(m4[ch], __uint_as_float(sv[ch][i]), __uint_as_float(sv[ch][i + 1]));
+        }
+        mx = fmaxf(fmax3(m4[0], m4[1], m4[2]), m4[3]);
       }
       // row maximum over both halves: exchange through shared memory with the partner warp (same rows)
       float* slot = xch + (j & 1) * 256;
@@ -333,6 +338,48 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_used = m_new;
         l *= alpha;
       }
+      // p = exp2(s*scale - m) as bf16 pairs, kept in registers: the exponentials need only S(j) and the maximum, so they
+      // run while the tensor core still works on P(j-1) V(j-1); tensor memory (the P columns, O) is touched after pv_done
+      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+      uint32_t pk[32];
+      // two copies of the loop: the common one (no tile edge, not on the diagonal) carries no compare/select per element
+      float l0 = 0.f, l1 = 0.f;
+      if (!need_mask) {
+        const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), m2 = pack_f32x2(-m_sub, -m_sub);
+        uint64_t l2 = pack_f32x2(0.f, 0.f);
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            float p0, p1;
+            const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sv[ch][i]), __uint_as_float(sv[ch][i + 1])), c2, m2);
+            if ((i >> 1) >= 8 - POLY) {                      // resolved at compile time (the loop is unrolled)
+              const uint64_t p2 = exp2_poly_f32x2(x2);
+              l2 = add_f32x2(l2, p2);
+              unpack_f32x2(p2, p0, p1);
+            } else {
+              float x0, x1;
+              unpack_f32x2(x2, x0, x1);
+              p0 = ex2f(x0); p1 = ex2f(x1);
+              l2 = add_f32x2(l2, pack_f32x2(p0, p1));
+            }
+            pk[ch * 8 + (i >> 1)] = pack_bf16(p0, p1);
+          }
+        }
+        unpack_f32x2(l2, l0, l1);
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const float p0 = (ch * 16 + i > kmax) ? 0.f : ex2f(fmaf(__uint_as_float(sv[ch][i]), p.scale_log2, -m_sub));
+            const float p1 = (ch * 16 + i + 1 > kmax) ? 0.f : ex2f(fmaf(__uint_as_float(sv[ch][i + 1]), p.scale_log2, -m_sub));
+            l0 += p0; l1 += p1;
+            pk[ch * 8 + (i >> 1)] = pack_bf16(p0, p1);
+          }
+        }
+      }
+      FWD_STAMP(wprof, j, 9);
       if (j > 0) {
         // PV(j-1) has read the previous P and finished updating O
         bool okp = mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, 702);
@@ -353,51 +400,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       FWD_STAMP(wprof, j, 8);
-      // p = exp2(s*scale - m); bf16 P (two per column) goes into the P columns: k-step 4*half+ch at column (4*half+ch)*8
-      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-      // two copies of the loop: the common one (no tile edge, not on the diagonal) carries no compare/select per element
-      float l0 = 0.f, l1 = 0.f;
-      if (!need_mask) {
-        const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2), m2 = pack_f32x2(-m_sub, -m_sub);
-        uint64_t l2 = pack_f32x2(0.f, 0.f);
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t pk[8];
-#pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            float p0, p1;
-            const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sv[ch][i]), __uint_as_float(sv[ch][i + 1])), c2, m2);
-            if ((i >> 1) >= 8 - POLY) {                      // resolved at compile time (the loop is unrolled)
-              const uint64_t p2 = exp2_poly_f32x2(x2);
-              l2 = add_f32x2(l2, p2);
-              unpack_f32x2(p2, p0, p1);
-            } else {
-              float x0, x1;
-              unpack_f32x2(x2, x0, x1);
-              p0 = ex2f(x0); p1 = ex2f(x1);
-              l2 = add_f32x2(l2, pack_f32x2(p0, p1));
-            }
-            pk[i >> 1] = pack_bf16(p0, p1);
-          }
-          tmem_st8(t_lane + P_COL + half * 32 + ch * 8, pk);
-        }
-        unpack_f32x2(l2, l0, l1);
-      } else {
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t pk[8];
-#pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            const float p0 = (ch * 16 + i > kmax) ? 0.f : ex2f(fmaf(__uint_as_float(sv[ch][i]), p.scale_log2, -m_sub));
-            const float p1 = (ch * 16 + i + 1 > kmax) ? 0.f : ex2f(fmaf(__uint_as_float(sv[ch][i + 1]), p.scale_log2, -m_sub));
-            l0 += p0; l1 += p1;
-            pk[i >> 1] = pack_bf16(p0, p1);
-          }
-          tmem_st8(t_lane + P_COL + half * 32 + ch * 8, pk);
-        }
-      }
+      // bf16 P into its columns: k-step 4*half+ch at column (4*half+ch)*8
+      tmem_st32(t_lane + P_COL + half * 32, pk);
       l += l0 + l1;
-      FWD_STAMP(wprof, j, 9);
       tmem_wait_st();
       tc_fence_before();
       FWD_STAMP(wprof, j, 10);
