@@ -113,6 +113,8 @@ def main() -> None:
     ap.add_argument("--cp", type=int, default=0, help="context-parallel degree (default: all GPUs); the rest is data parallel")
     ap.add_argument("--yarn-scale", type=float, default=1.0, help="YaRN position-scaling factor (1 = plain RoPE)")
     ap.add_argument("--recompute", default="selective")
+    ap.add_argument("--env", nargs="*", default=[], metavar="KEY=VALUE", help="further settings of the CP_* environment surface, "
+                                                                              "e.g. CP_SHARE_FWD_ROTATOR=1 CP_DKV_MODE=pull")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the ring timing and the cp_parity step (N > 1)")
     ap.add_argument("--phases", action="store_true", help="after the timed steps run one more step with every kernel launch "
@@ -147,6 +149,7 @@ def main() -> None:
     cp = args.cp or world
     dp = world // cp
     env = {"CP_SIZE": str(cp)}
+    env.update(kv.split("=", 1) for kv in args.env)
     if args.yarn_scale != 1.0:
         env.update(YARN_SCALE=str(args.yarn_scale), YARN_ORIG_MAXPOS=str(args.T / args.yarn_scale))
     tokens_per_step = args.batch * args.T * dp
@@ -299,7 +302,7 @@ def main() -> None:
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.batch * dp, "seq_len": args.T, "yarn_scale": args.yarn_scale,
                        "parallelism": par, "rotator": args.rotator if world > 1 else "none",
-                       "recompute": args.recompute, "l2": "inputs larger than L2 (activations are GBs per layer)",
+                       "recompute": args.recompute, "env": sorted(args.env), "l2": "inputs larger than L2 (activations are GBs per layer)",
                        "optimizer_step_in_timed_region": True},
             "model_tflops_per_gpu": flops / (ms / args.steps / 1e3) / world / 1e12,
             "attn_share_of_flops": attn_flops / flops,

@@ -91,6 +91,18 @@ __device__ __forceinline__ void umma_pair_commit_p(uint32_t leader, uint32_t clu
       ::"r"(cluster_addr), "r"(leader) : "memory");
 }
 
+// Tile order: bands of `band` pair-rows swept along N, rows fastest.  With band = 8 the 74 pairs running at one time
+// share 8 row tiles of A and about 9 column tiles of B, and successive waves keep the band's A rows in L2, so a GEMM
+// whose B operand does not fit in L2 beside A's band (8192^3: 134 MB against 126 MB) streams B once per band instead of
+// once per 2.3 rows of tiles.  band = 1 is the plain order (columns fastest), kept while B stays resident anyway.
+__device__ __forceinline__ void pair_tile_coords(int tile, int num_m_tiles, int num_n_blocks, int band_rows, int& mt, int& nb) {
+  const int per_band = band_rows * num_n_blocks;
+  const int band = tile / per_band, idx = tile - band * per_band;
+  const int rows = min(band_rows, num_m_tiles - band * band_rows);
+  nb = idx / rows;
+  mt = band * band_rows + (idx - nb * rows);
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
@@ -135,8 +147,9 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tma_prefetch_desc(&tmB);
       int stage = 0; uint32_t phase = 0;
       for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-        const int m0 = (tile / p.num_n_blocks) * (2 * GEMM_BM) + (int)rank * GEMM_BM;      // this CTA's rows
-        const int nb = tile % p.num_n_blocks;
+        int mt, nb;
+        pair_tile_coords(tile, num_m_tiles, p.num_n_blocks, p.band, mt, nb);
+        const int m0 = mt * (2 * GEMM_BM) + (int)rank * GEMM_BM;      // this CTA's rows
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 110)) break;
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
@@ -211,8 +224,9 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (tile / p.num_n_blocks) * (2 * GEMM_BM) + (int)rank * GEMM_BM;
-      const int nb = tile % p.num_n_blocks;
+      int mt, nb;
+      pair_tile_coords(tile, num_m_tiles, p.num_n_blocks, p.band, mt, nb);
+      const int m0 = mt * (2 * GEMM_BM) + (int)rank * GEMM_BM;
       bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 310);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;

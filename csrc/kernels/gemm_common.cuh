@@ -24,6 +24,7 @@ struct GemmParams {
   int epi;
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int swiglu_half;     // number of output features F when epi == SWIGLU (B has 2F rows)
+  int band;            // CTA-pair kernel: pair-rows per band of the tile order (1 = rows of tiles, columns fastest)
   void* C;
   void* aux;
   const float* bias;

@@ -34,6 +34,23 @@ def test_gemm_majors(M, N, K, a_mn, b_mn):
     assert_close(got.float(), want, cos=0.9999, rel=2e-2, name=f"gemm {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}")
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm_pair_banded_order(a_mn, b_mn):
+    """A B operand above 64 MB switches the CTA-pair kernel to its banded tile order (8 pair-rows per band, a ragged last
+    band here: 11 pair-rows); every output tile must still be produced exactly once."""
+    from context_parallelism_b200.ops.gemm import gemm
+    torch.manual_seed(3)
+    M, N, K = 2816 - 8, 8192, 4160
+    A = torch.randn(M, K, device=dev()).bfloat16()
+    B = (torch.randn(N, K, device=dev()) * 0.1).bfloat16()
+    want = A.float() @ B.float().t()
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    got = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    check_status()
+    assert_close(got.float(), want, cos=0.9999, rel=2e-2, name=f"banded gemm a_mn={a_mn} b_mn={b_mn}")
+
+
 def test_gemm_epilogues():
     from context_parallelism_b200.ops import gemm as G
     torch.manual_seed(1)
