@@ -19,9 +19,9 @@ def hybrid_attention(q, k, v, ctx, attn, fused: bool):
     U, R = ctx.ulysses_size, ctx.ring_size
     if q.shape[2] % U or k.shape[2] % U:
         raise ValueError("hybrid: q_heads and kv_heads must be multiples of the Ulysses degree")
-    # The peer-memory Ulysses exchange around the ring is selected with CP_FUSED_HYBRID_ULYSSES=1; the default is the
-    # NCCL all-to-all on the Ulysses axis with the fused ring on the ring axis.
-    fused_uly = (fused and U > 1 and os.environ.get("CP_FUSED_HYBRID_ULYSSES", "0") == "1"
+    # With the fused transport both axes go over peer memory: the sequence<->head exchange on the Ulysses axis around the
+    # fused ring on the ring axis.  CP_FUSED_HYBRID_ULYSSES=0 keeps the NCCL all-to-all on the Ulysses axis.
+    fused_uly = (fused and U > 1 and os.environ.get("CP_FUSED_HYBRID_ULYSSES", "1") == "1"
                  and getattr(ctx.fused, "g_uly", None) is not None and q.dtype == torch.bfloat16)
     ub = None
     dbg = getattr(attn, "dbg", None)

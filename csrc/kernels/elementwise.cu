@@ -31,6 +31,17 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
 }
 
+// eight consecutive fp32 parameters (vector c of a row) as two 16-byte loads; `fill` when the parameter is absent
+__device__ __forceinline__ void load8f(const float* __restrict__ p, int c, float fill, float (&f)[8]) {
+  if (p == nullptr) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = fill;
+    return;
+  }
+  const float4 a = __ldg((const float4*)p + 2 * c), b = __ldg((const float4*)p + 2 * c + 1);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
 // ============================================================================ norm forward
 // One warp per row; d % 8 == 0; MAXV = max 16-byte vectors per lane (d <= 256*MAXV).
 // If `res` != null: x_new = x + res is written to `xout` and normalised.
@@ -46,26 +57,35 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
   const int nvec = d >> 3;
   const uint4* xr = (const uint4*)(x + (size_t)row * d);
   const uint4* rr = res ? (const uint4*)(res + (size_t)row * d) : nullptr;
-  float v[MAXV][8];
+  // every load of the row is issued before the first use; the row then stays in registers as bf16 (the rounded x + res,
+  // exactly what later kernels re-read)
+  uint4 px[MAXV], pr[MAXV];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = lane + i * 32;
+    if (c < nvec) {
+      px[i] = xr[c];
+      if (rr) pr[i] = rr[c];
+    }
+  }
   float s = 0.f, ss = 0.f;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     const int c = lane + i * 32;
     if (c < nvec) {
-      uint4 u = xr[c];
-      unpack8(u, v[i]);
+      float v[8];
+      unpack8(px[i], v);
       if (rr) {
         float r8[8];
-        uint4 ur = rr[c];
-        unpack8(ur, r8);
+        unpack8(pr[i], r8);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] += r8[j];
-        uint4 o = pack8(v[i]);
-        ((uint4*)(xout + (size_t)row * d))[c] = o;
-        unpack8(o, v[i]);      // normalise exactly what later kernels will re-read
+        for (int j = 0; j < 8; ++j) v[j] += r8[j];
+        px[i] = pack8(v);
+        ((uint4*)(xout + (size_t)row * d))[c] = px[i];
+        unpack8(px[i], v);
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { s += v[i][j]; ss += v[i][j] * v[i][j]; }
+      for (int j = 0; j < 8; ++j) { s += v[j]; ss += v[j] * v[j]; }
     }
   }
   s = warp_sum(s); ss = warp_sum(ss);
@@ -82,12 +102,12 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
   for (int i = 0; i < MAXV; ++i) {
     const int c = lane + i * 32;
     if (c < nvec) {
-      float o[8];
+      float v[8], o[8], g[8], bb[8];
+      unpack8(px[i], v);
+      load8f(w, c, 1.f, g);
+      if (LAYER) load8f(b, c, 0.f, bb);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float g = w ? w[c * 8 + j] : 1.f;
-        o[j] = (v[i][j] - mean) * rstd * g + ((LAYER && b) ? b[c * 8 + j] : 0.f);
-      }
+      for (int j = 0; j < 8; ++j) o[j] = (v[j] - mean) * rstd * g[j] + (LAYER ? bb[j] : 0.f);
       ((uint4*)(y + (size_t)row * d))[c] = pack8(o);
     }
   }
@@ -98,45 +118,57 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
 // Each block handles `rows_per_block` rows with one warp per row in a loop and reduces dw/db through
 // shared memory before one atomicAdd per column per block.
 template <bool LAYER, int MAXV>
-__global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
-                                const __nv_bfloat16* __restrict__ dres, const float* __restrict__ w,
-                                const float* __restrict__ stats, __nv_bfloat16* __restrict__ dx,
-                                float* __restrict__ dw, float* __restrict__ db, int rows, int d, int rows_per_block) {
-  extern __shared__ float sm[];          // [2][d]
+__global__ void __launch_bounds__(256, 2)
+norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                const __nv_bfloat16* __restrict__ dres, const float* __restrict__ w,
+                const float* __restrict__ stats, __nv_bfloat16* __restrict__ dx,
+                float* __restrict__ dw, float* __restrict__ db, int rows, int d, int rows_per_block) {
+  extern __shared__ float sm[];          // [2][d]: the block's partial dw, db
   float* sdw = sm;
   float* sdb = sm + d;
   for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) sm[i] = 0.f;
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int nvec = d >> 3;
-  float adw[MAXV][8], adb[MAXV][8];
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { adw[i][j] = 0.f; adb[i][j] = 0.f; }
+  const int rot = lane >> 2;             // shared-memory adds start at element `rot` of every vector: conflict-free banks
   const int r0 = blockIdx.x * rows_per_block;
   const int r1 = min(rows, r0 + rows_per_block);
   for (int row = r0 + warp; row < r1; row += nwarps) {
     const float mean = LAYER ? stats[2 * (size_t)row] : 0.f;
     const float rstd = stats[2 * (size_t)row + 1];
-    float xh[MAXV][8], g[MAXV][8];
+    // the row stays in registers as it was loaded (bf16, 4 registers per 8 elements); every load is issued before the
+    // first use, and the weight-gradient partials go to shared memory row by row, so that two blocks fit on an SM and
+    // enough bytes are in flight to cover the memory latency
+    uint4 px[MAXV], pd[MAXV], pr[MAXV];
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        px[i] = ((const uint4*)(x + (size_t)row * d))[c];
+        pd[i] = ((const uint4*)(dy + (size_t)row * d))[c];
+        if (dres) pr[i] = ((const uint4*)(dres + (size_t)row * d))[c];
+      }
+    }
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < MAXV; ++i) {
       const int c = lane + i * 32;
       if (c < nvec) {
-        float xv[8], dv[8];
-        uint4 ux = ((const uint4*)(x + (size_t)row * d))[c];
-        uint4 ud = ((const uint4*)(dy + (size_t)row * d))[c];
-        unpack8(ux, xv); unpack8(ud, dv);
+        float xv[8], dv[8], wv[8];
+        unpack8(px[i], xv); unpack8(pd[i], dv);
+        load8f(w, c, 1.f, wv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          xh[i][j] = (xv[j] - mean) * rstd;
-          g[i][j] = dv[j] * (w ? w[c * 8 + j] : 1.f);
-          s1 += g[i][j] * xh[i][j];
-          s2 += g[i][j];
-          adw[i][j] += dv[j] * xh[i][j];
-          adb[i][j] += dv[j];
+          const float xh = (xv[j] - mean) * rstd, g = dv[j] * wv[j];
+          s1 += g * xh;
+          s2 += g;
+          xv[j] = dv[j] * xh;
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const int j = (jj + rot) & 7;
+          if (dw) atomicAdd(&sdw[c * 8 + j], xv[j]);
+          if (LAYER && db) atomicAdd(&sdb[c * 8 + j], dv[j]);
         }
       }
     }
@@ -146,26 +178,17 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
     for (int i = 0; i < MAXV; ++i) {
       const int c = lane + i * 32;
       if (c < nvec) {
-        float o[8];
-        float r8[8];
-        if (dres) { uint4 ur = ((const uint4*)(dres + (size_t)row * d))[c]; unpack8(ur, r8); }
+        float xv[8], dv[8], wv[8], r8[8], o[8];
+        unpack8(px[i], xv); unpack8(pd[i], dv);
+        load8f(w, c, 1.f, wv);
+        if (dres) unpack8(pr[i], r8);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          o[j] = rstd * (g[i][j] - xh[i][j] * s1 - s2);
+          const float xh = (xv[j] - mean) * rstd, g = dv[j] * wv[j];
+          o[j] = rstd * (g - xh * s1 - s2);
           if (dres) o[j] += r8[j];
         }
         ((uint4*)(dx + (size_t)row * d))[c] = pack8(o);
-      }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int c = lane + i * 32;
-    if (c < nvec) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (dw) atomicAdd(&sdw[c * 8 + j], adw[i][j]);
-        if (LAYER && db) atomicAdd(&sdb[c * 8 + j], adb[i][j]);
       }
     }
   }

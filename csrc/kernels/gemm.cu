@@ -197,9 +197,9 @@ extern "C" int cpb_gemm_bf16(const void* A, const void* B, void* C, void* aux, c
   p.num_m_blocks = (M + GEMM_BM - 1) / GEMM_BM;
   p.num_k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
   p.swiglu_half = (epi == EPI_BF16_SWIGLU) ? N : 0;
-  // banded tile order of the pair kernel once B (N x K bf16) no longer stays in L2 by itself; CPB_GEMM_BAND (read once) overrides
+  // banded tile order of the pair kernel once B (N x K bf16) reaches 64 MB, half of L2; CPB_GEMM_BAND (read once) overrides
   static const int band_env = [] { const char* e = getenv("CPB_GEMM_BAND"); return e ? atoi(e) : 0; }();
-  p.band = band_env > 0 ? band_env : (((size_t)N * K * 2 > ((size_t)64 << 20)) ? 8 : 1);
+  p.band = band_env > 0 ? band_env : (((size_t)N * K * 2 >= ((size_t)64 << 20)) ? 8 : 1);
   p.num_n_blocks = (epi == EPI_BF16_SWIGLU) ? (N + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
   p.C = C; p.aux = aux; p.bias = bias; p.status = status;
 

@@ -41,9 +41,11 @@ def test_ring_fused_gpt2_recompute_2gpu():
                "--recompute", "selective", device="cuda")
 
 
-def test_hybrid_fused_ulysses_exchange_2gpu(monkeypatch):
-    """Hybrid with Ulysses degree 2 and ring degree 1: the peer-memory sequence<->head exchange around the local attention."""
-    monkeypatch.setenv("CP_FUSED_HYBRID_ULYSSES", "1")
+@pytest.mark.parametrize("peer_exchange", ["1", "0"])
+def test_hybrid_fused_ulysses_exchange_2gpu(monkeypatch, peer_exchange):
+    """Hybrid with Ulysses degree 2 and ring degree 1: the peer-memory sequence<->head exchange around the local attention
+    (the default) and the NCCL all-to-all on the Ulysses axis."""
+    monkeypatch.setenv("CP_FUSED_HYBRID_ULYSSES", peer_exchange)
     run_worker(2, "--mode", "hybrid", "--ulysses", 2, "--rotator", "fused", "--T", 1024, "--tol", TOL, device="cuda")
 
 
