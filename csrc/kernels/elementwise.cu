@@ -375,7 +375,7 @@ __device__ __forceinline__ void load8_f32(const float* p, float (&v)[8]) {
 }
 
 template <int D>
-__global__ void qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+__global__ void __launch_bounds__(256, 3) qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                                         const float* __restrict__ gq, const float* __restrict__ gk,
                                         const float* __restrict__ cache, const int64_t* __restrict__ pos,
                                         float* __restrict__ rstd, size_t rows, int T, int Hq, int Hkv, float eps,
@@ -389,45 +389,64 @@ __global__ void qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, __
   const int eh = (gl % (GL / 2)) * 8;               // the same position inside a half (index into cos / sin)
   const size_t nvec = rows * H;
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
-  for (size_t w0 = (blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5)) * VPW; w0 < nvec; w0 += warps * VPW) {
-    const size_t w = w0 + lane / GL;
-    const bool live = w < nvec;
-    const size_t row = live ? w / H : 0;
-    const int h = live ? (int)(w % H) : H - 1;
-    float x[8];
-    if (live) { uint4 u = *(const uint4*)(in + w * D + e0); unpack8(u, x); }
-    else {
+  const bool small = nvec < 0x7fffffffu;            // 32-bit index arithmetic (a 64-bit division costs about a hundred instructions)
+  constexpr int U = 4;                              // head vectors per lane and pass: their loads are all issued before the first use
+  for (size_t w0 = (blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5)) * VPW; w0 < nvec; w0 += warps * VPW * U) {
+    size_t w[U];
+    bool live[U];
+    int h[U];
+    uint32_t trow[U];                               // token index inside the sequence (row % T)
+    size_t row[U];
+    uint4 raw[U];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] = 0.f;
+    for (int u = 0; u < U; ++u) {
+      w[u] = w0 + (size_t)u * warps * VPW + lane / GL;
+      live[u] = w[u] < nvec;
+      if (small) {
+        const uint32_t wi = live[u] ? (uint32_t)w[u] : 0u, r = wi / (uint32_t)H;
+        row[u] = r; h[u] = live[u] ? (int)(wi - r * (uint32_t)H) : H - 1; trow[u] = r % (uint32_t)T;
+      } else {
+        row[u] = live[u] ? w[u] / H : 0; h[u] = live[u] ? (int)(w[u] % H) : H - 1; trow[u] = (uint32_t)(row[u] % T);
+      }
+      raw[u] = live[u] ? *(const uint4*)(in + w[u] * D + e0) : make_uint4(0, 0, 0, 0);
     }
-    const bool rot = h < Hq + Hkv;                  // uniform inside a lane group
-    const float* gamma = h < Hq ? gq : gk;
-    float ss = 0.f;
+    const float* cr[U];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
-    ss = group_sum<D>(ss);
-    if (rot && gamma) {
-      const float r = rsqrtf(ss / D + eps);
-      if (rstd && gl == 0 && live) rstd[row * (size_t)(Hq + Hkv) + h] = r;
-      float g[8];
-      load8_f32(gamma + e0, g);
+    for (int u = 0; u < U; ++u) {
+      cr[u] = nullptr;
+      if (h[u] < Hq + Hkv && cache && live[u]) {
+        const int64_t p = pos[trow[u]];
+        if (p >= 0 && p < cache_len) cr[u] = cache + (size_t)p * D;
+        else report(status, ST_BAD_INDEX, 400, (int)p);
+      }
+    }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] = x[i] * r * g[i];
-    }
-    const float* cr = nullptr;
-    if (rot && cache && live) {
-      const int64_t p = pos[row % T];
-      if (p >= 0 && p < cache_len) cr = cache + (size_t)p * D;
-      else report(status, ST_BAD_INDEX, 400, (int)p);
-    }
-    float c[8], sn[8];
-    if (cr) { load8_f32(cr + eh, c); load8_f32(cr + half + eh, sn); }
+    for (int u = 0; u < U; ++u) {
+      float x[8];
+      unpack8(raw[u], x);
+      const bool rot = h[u] < Hq + Hkv;               // uniform inside a lane group
+      const float* gamma = h[u] < Hq ? gq : gk;
+      float c[8], sn[8];
+      if (cr[u]) { load8_f32(cr[u] + eh, c); load8_f32(cr[u] + half + eh, sn); }
+      float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float other = __shfl_xor_sync(0xffffffffu, x[i], GL / 2);      // the paired element of the other half
-      if (cr) x[i] = second ? other * sn[i] + x[i] * c[i] : x[i] * c[i] - other * sn[i];
+      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+      ss = group_sum<D>(ss);
+      if (rot && gamma) {
+        const float r = rsqrtf(ss / D + eps);
+        if (rstd && gl == 0 && live[u]) rstd[row[u] * (size_t)(Hq + Hkv) + h[u]] = r;
+        float g[8];
+        load8_f32(gamma + e0, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = x[i] * r * g[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[i], GL / 2);      // the paired element of the other half
+        if (cr[u]) x[i] = second ? other * sn[i] + x[i] * c[i] : x[i] * c[i] - other * sn[i];
+      }
+      if (live[u]) *(uint4*)(out + w[u] * D + e0) = pack8(x);
     }
-    if (live) *(uint4*)(out + w * D + e0) = pack8(x);
   }
 }
 
