@@ -31,6 +31,7 @@ The NCCL rotators, ``all_to_all_single`` and ``all_reduce`` (``parallel.ring``, 
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 from typing import Dict, List, Optional, Tuple
 
@@ -45,6 +46,13 @@ from ..utils.debug import DebugTools
 from .symm import SymmetricHeap, tensor_from_ptr
 
 N_COPY_CTAS = 16
+
+
+@functools.lru_cache(maxsize=None)
+def _gather_ctas(device) -> int:
+    """CTAs of a stand-alone K/V gather (nothing else runs beside it): two per SM, so that enough peer loads are in flight to
+    cover the NVLink latency."""
+    return 2 * torch.cuda.get_device_properties(device).multi_processor_count
 FLAG_BYTES = 4096
 
 
@@ -416,7 +424,7 @@ def ring_fwd_compute(fc: FusedComm, rb: _RingBuffers, slot: int, q, pos32, scale
     segs = rb.segs(fc, slot)
     if fc.no_overlap_fwd:
         # diagnostics (CP_NO_OVERLAP[_FWD]): the gather is a launch of its own that finishes before attention starts
-        nv.call("ring_gather", nv.ptr(segs), nv.i(segs.shape[0]), nv.ptr(rb.ready_bwd), nv.i(4 * N_COPY_CTAS), nv.stream_ptr(q.device))
+        nv.call("ring_gather", nv.ptr(segs), nv.i(segs.shape[0]), nv.ptr(rb.ready_bwd), nv.i(_gather_ctas(q.device)), nv.stream_ptr(q.device))
         return A.flash_fwd(q, rb.gathered[0], rb.gathered[1], scale, True, pos32, 0)
     rb.gather_calls += 1
     return A.flash_fwd(q, rb.gathered[0], rb.gathered[1], scale, True, pos32, 0,
@@ -452,7 +460,7 @@ def ring_bwd_compute(fc: FusedComm, rb: _RingBuffers, slot: int, q, out, lse, do
     dev = q.device
     B, Tl, Hq, D = q.shape
     segs = rb.segs(fc, slot)
-    nv.call("ring_gather", nv.ptr(segs), nv.i(segs.shape[0]), nv.ptr(rb.ready_bwd), nv.i(4 * N_COPY_CTAS), nv.stream_ptr(dev))
+    nv.call("ring_gather", nv.ptr(segs), nv.i(segs.shape[0]), nv.ptr(rb.ready_bwd), nv.i(_gather_ctas(dev)), nv.stream_ptr(dev))
     delta, lse2 = AB.flash_bwd_prep(out, do, lse)
     qpos_pad = AB.padded_q_pos(Tl, dev, pos32)
     dq = torch.zeros((B, Tl, Hq, D), dtype=torch.float32, device=dev)

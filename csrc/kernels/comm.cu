@@ -110,33 +110,37 @@ struct A2APullParams {
 };
 
 // head -> sequence: every rank pulls, for its own Tl tokens, each head from the rank(s) that own it in the
-// head-sharded layout [B, P*Tl, src_heads, D], summing KV replicas in fp32.  One warp per (b, t, part, head).
+// head-sharded layout [B, P*Tl, src_heads, D], summing KV replicas in fp32.  One group of D/8 lanes per (b, t, part, head).
 __global__ void a2a_pull_kernel(A2APullParams p) {
   const int lane = threadIdx.x & 31;
   int heads_total = 0;
   for (int i = 0; i < p.n_parts; ++i) heads_total += p.part[i].n_heads;
   const size_t n_items = (size_t)p.B * p.Tl * heads_total;
   const int vec_per_head = p.D / 8;
-  for (size_t w = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); w < n_items; w += (size_t)gridDim.x * (blockDim.x >> 5)) {
+  // a warp covers 32 / vec_per_head heads per pass (four at head_dim 64): every lane carries a 16-byte peer load
+  const int ipw = 32 / vec_per_head, sub = lane / vec_per_head, c = lane % vec_per_head;
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t w0 = (blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5)) * ipw; w0 < n_items; w0 += warps * ipw) {
+    const size_t w = w0 + sub;
+    if (sub >= ipw || w >= n_items) continue;
     int hh = (int)(w % heads_total);
     const int t = (int)((w / heads_total) % p.Tl);
     const int b = (int)(w / ((size_t)heads_total * p.Tl));
     int pi = 0;
     while (hh >= p.part[pi].n_heads) { hh -= p.part[pi].n_heads; ++pi; }
     const A2APullPart& a = p.part[pi];
-    if (lane >= vec_per_head) continue;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int rr = 0; rr < a.rep; ++rr) {
       const int peer = a.rep > 1 ? hh * a.rep + rr : hh / a.n_local;
       const int j = a.rep > 1 ? 0 : hh % a.n_local;
       const uint4* src_row = (const uint4*)(p.peers[peer] + a.src_off) +
                              (((size_t)b * p.P * p.Tl + (size_t)p.my_rank * p.Tl + t) * a.src_heads) * vec_per_head;
-      const uint4 v = src_row[(size_t)(a.src_head_off + j) * vec_per_head + lane];
+      const uint4 v = src_row[(size_t)(a.src_head_off + j) * vec_per_head + c];
       acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
       acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
     }
     uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
-    *((uint4*)(a.dst + ((size_t)b * p.Tl + t) * a.dst_tok_stride + (size_t)hh * p.D) + lane) = o;
+    *((uint4*)(a.dst + ((size_t)b * p.Tl + t) * a.dst_tok_stride + (size_t)hh * p.D) + c) = o;
   }
 }
 
@@ -241,12 +245,28 @@ __global__ void allgather_pull_kernel(const uint64_t* __restrict__ peers, long b
   const GatherSeg sg = segs[blockIdx.y];
   const int epv = 16 / elem_bytes;                          // elements per 16-byte vector
   const long nvec = sg.elem_n / epv;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
-    const long e = sg.elem_start + i * epv;
-    const int owner = (int)((e - sg.bucket_start) / sg.per);
-    if (owner == my_rank || owner >= world) continue;
-    const long v = ((e - buf_elem0) * elem_bytes) >> 4;
-    *((uint4*)(peers[my_rank] + buf_off) + v) = *((const uint4*)(peers[owner] + buf_off) + v);
+  const long stride = (long)gridDim.x * blockDim.x;
+  const long seg_off = sg.elem_start - sg.bucket_start;     // a bucket has far fewer than 2^31 elements: 32-bit ownership math
+  uint4* mine = (uint4*)(peers[my_rank] + buf_off);
+  constexpr int U = 8;                                      // eight peer loads in flight per thread before the first store
+  for (long i0 = blockIdx.x * (long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    uint4 v[U];
+    long at[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long i = i0 + u * stride;
+      at[u] = -1;
+      if (i < nvec) {
+        const int owner = (int)((uint32_t)(seg_off + i * epv) / (uint32_t)sg.per);
+        if (owner != my_rank && owner < world) {
+          at[u] = ((sg.elem_start + i * epv - buf_elem0) * elem_bytes) >> 4;
+          v[u] = *((const uint4*)(peers[owner] + buf_off) + at[u]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (at[u] >= 0) mine[at[u]] = v[u];
   }
 }
 

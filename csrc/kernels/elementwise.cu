@@ -374,161 +374,163 @@ __device__ __forceinline__ void load8_f32(const float* p, float (&v)[8]) {
   v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
+// One warp per token row: the row's cos / sin values (this lane's 8 positions inside a half) and its position are
+// loaded once and reused for every q and k head of the row; without that reuse each head re-reads its 2 * D floats of the
+// cache row, as many bytes as the packed QKV itself.  The heads of the row are swept 32 * 8 / D at a time, U sweeps' loads
+// issued before the first use.
 template <int D>
 __global__ void __launch_bounds__(256, 3) qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                                         const float* __restrict__ gq, const float* __restrict__ gk,
                                         const float* __restrict__ cache, const int64_t* __restrict__ pos,
                                         float* __restrict__ rstd, size_t rows, int T, int Hq, int Hkv, float eps,
                                         int cache_len, int* status) {
-  constexpr int GL = D / 8, VPW = 32 / GL, half = D / 2;
+  constexpr int GL = D / 8, VPW = 32 / GL, half = D / 2, U = 4;
   const int H = Hq + 2 * Hkv;
   const int lane = threadIdx.x & 31;
   const int gl = lane % GL;                         // lane inside its vector's group
+  const int hv = lane / GL;                         // which of the VPW heads of a sweep this lane works on
   const bool second = gl >= GL / 2;                 // this lane holds elements of the second half
   const int e0 = gl * 8;                            // first element this lane holds
   const int eh = (gl % (GL / 2)) * 8;               // the same position inside a half (index into cos / sin)
-  const size_t nvec = rows * H;
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
-  const bool small = nvec < 0x7fffffffu;            // 32-bit index arithmetic (a 64-bit division costs about a hundred instructions)
-  constexpr int U = 4;                              // head vectors per lane and pass: their loads are all issued before the first use
-  for (size_t w0 = (blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5)) * VPW; w0 < nvec; w0 += warps * VPW * U) {
-    size_t w[U];
-    bool live[U];
-    int h[U];
-    uint32_t trow[U];                               // token index inside the sequence (row % T)
-    size_t row[U];
-    uint4 raw[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      w[u] = w0 + (size_t)u * warps * VPW + lane / GL;
-      live[u] = w[u] < nvec;
-      if (small) {
-        const uint32_t wi = live[u] ? (uint32_t)w[u] : 0u, r = wi / (uint32_t)H;
-        row[u] = r; h[u] = live[u] ? (int)(wi - r * (uint32_t)H) : H - 1; trow[u] = r % (uint32_t)T;
+  float gqv[8], gkv[8];
+  if (gq) load8_f32(gq + e0, gqv);
+  if (gk) load8_f32(gk + e0, gkv);
+  for (size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+    float c[8], sn[8];
+    bool have_cs = false;
+    if (cache) {
+      const int64_t p = pos[row % T];
+      if (p >= 0 && p < cache_len) {
+        const float* cr = cache + (size_t)p * D;
+        load8_f32(cr + eh, c); load8_f32(cr + half + eh, sn);
+        have_cs = true;
       } else {
-        row[u] = live[u] ? w[u] / H : 0; h[u] = live[u] ? (int)(w[u] % H) : H - 1; trow[u] = (uint32_t)(row[u] % T);
-      }
-      raw[u] = live[u] ? *(const uint4*)(in + w[u] * D + e0) : make_uint4(0, 0, 0, 0);
-    }
-    const float* cr[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      cr[u] = nullptr;
-      if (h[u] < Hq + Hkv && cache && live[u]) {
-        const int64_t p = pos[trow[u]];
-        if (p >= 0 && p < cache_len) cr[u] = cache + (size_t)p * D;
-        else report(status, ST_BAD_INDEX, 400, (int)p);
+        report(status, ST_BAD_INDEX, 400, (int)p);
       }
     }
+    const __nv_bfloat16* irow = in + row * (size_t)H * D;
+    __nv_bfloat16* orow = out + row * (size_t)H * D;
+    for (int h0 = 0; h0 < H; h0 += VPW * U) {
+      uint4 raw[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      float x[8];
-      unpack8(raw[u], x);
-      const bool rot = h[u] < Hq + Hkv;               // uniform inside a lane group
-      const float* gamma = h[u] < Hq ? gq : gk;
-      float c[8], sn[8];
-      if (cr[u]) { load8_f32(cr[u] + eh, c); load8_f32(cr[u] + half + eh, sn); }
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
-      ss = group_sum<D>(ss);
-      if (rot && gamma) {
-        const float r = rsqrtf(ss / D + eps);
-        if (rstd && gl == 0 && live[u]) rstd[row[u] * (size_t)(Hq + Hkv) + h[u]] = r;
-        float g[8];
-        load8_f32(gamma + e0, g);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = x[i] * r * g[i];
+      for (int u = 0; u < U; ++u) {
+        const int h = h0 + u * VPW + hv;
+        raw[u] = h < H ? *(const uint4*)(irow + (size_t)h * D + e0) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float other = __shfl_xor_sync(0xffffffffu, x[i], GL / 2);      // the paired element of the other half
-        if (cr[u]) x[i] = second ? other * sn[i] + x[i] * c[i] : x[i] * c[i] - other * sn[i];
+      for (int u = 0; u < U; ++u) {
+        const int h = h0 + u * VPW + hv;
+        const bool live = h < H;
+        const bool rot = live && h < Hq + Hkv;          // uniform inside a lane group
+        const bool isq = h < Hq;
+        float x[8];
+        unpack8(raw[u], x);
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+        ss = group_sum<D>(ss);
+        if (rot && (isq ? gq != nullptr : gk != nullptr)) {
+          const float r = rsqrtf(ss / D + eps);
+          if (rstd && gl == 0) rstd[row * (size_t)(Hq + Hkv) + h] = r;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[i] = x[i] * r * (isq ? gqv[i] : gkv[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, x[i], GL / 2);      // the paired element of the other half
+          if (rot && have_cs) x[i] = second ? other * sn[i] + x[i] * c[i] : x[i] * c[i] - other * sn[i];
+        }
+        if (live) *(uint4*)(orow + (size_t)h * D + e0) = pack8(x);
       }
-      if (live[u]) *(uint4*)(out + w[u] * D + e0) = pack8(x);
     }
   }
 }
 
-// Backward: given d(out) and the pre-norm input, produce d(in) and accumulate dgamma_q / dgamma_k.
-//   y = R(xhat * gamma), xhat = x * rstd
-//   dz = R^T dy ; dgamma += dz * xhat ; dxhat = dz * gamma ; dx = rstd * (dxhat - xhat * mean(dxhat * xhat))
+// Backward of the above on the packed gradient: din = d(in); dgq / dgk (fp32, +=) accumulate the gain gradients.
+// `in` is the ORIGINAL (pre-norm, pre-rotation) packed QKV.  Same row-per-warp sweep as the forward kernel.
 template <int D>
-__global__ void qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dout,
+__global__ void __launch_bounds__(256, 2) qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dout,
                                         __nv_bfloat16* __restrict__ din, const float* __restrict__ gq,
                                         const float* __restrict__ gk, const float* __restrict__ cache,
                                         const int64_t* __restrict__ pos, float* __restrict__ dgq, float* __restrict__ dgk,
                                         size_t rows, int T, int Hq, int Hkv, float eps, int cache_len) {
-  constexpr int GL = D / 8, VPW = 32 / GL, half = D / 2;
+  constexpr int GL = D / 8, VPW = 32 / GL, half = D / 2, U = 2;
   __shared__ float sg[2][D];
   for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&sg[0][0])[i] = 0.f;
   __syncthreads();
   const int H = Hq + 2 * Hkv;
   const int lane = threadIdx.x & 31;
-  const int gl = lane % GL;
+  const int gl = lane % GL, hv = lane / GL;
   const bool second = gl >= GL / 2;
   const int e0 = gl * 8, eh = (gl % (GL / 2)) * 8;
-  const size_t nvec = rows * H;
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
-  float accq[8], acck[8];
+  float accq[8], acck[8], gqv[8], gkv[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) accq[i] = acck[i] = 0.f;
-  for (size_t w0 = (blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5)) * VPW; w0 < nvec; w0 += warps * VPW) {
-    const size_t w = w0 + lane / GL;
-    const bool live = w < nvec;
-    const size_t row = live ? w / H : 0;
-    const int h = live ? (int)(w % H) : H - 1;
-    float d[8];
-    if (live) { uint4 u = *(const uint4*)(dout + w * D + e0); unpack8(u, d); }
-    else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) d[i] = 0.f;
-    }
-    const bool rot = h < Hq + Hkv;
-    const float* g = h < Hq ? gq : gk;
-    const float* cr = nullptr;
-    if (rot && cache && live) {
-      const int64_t p = pos[row % T];
-      if (p >= 0 && p < cache_len) cr = cache + (size_t)p * D;
-    }
+  if (gq) load8_f32(gq + e0, gqv);
+  if (gk) load8_f32(gk + e0, gkv);
+  for (size_t row = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
     float c[8], sn[8];
-    if (cr) { load8_f32(cr + eh, c); load8_f32(cr + half + eh, sn); }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float other = __shfl_xor_sync(0xffffffffu, d[i], GL / 2);
-      if (cr) d[i] = second ? d[i] * c[i] - other * sn[i] : d[i] * c[i] + other * sn[i];     // transpose of the rotation
-    }
-    float xh[8];
-    if (live && rot && g) { uint4 u = *(const uint4*)(in + w * D + e0); unpack8(u, xh); }
-    else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) xh[i] = 0.f;
-    }
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ss += xh[i] * xh[i];
-    ss = group_sum<D>(ss);
-    // every shuffle below is executed by the whole warp: lane groups of one warp may hold different kinds of heads
-    const bool normed = rot && g != nullptr;
-    const float r = rsqrtf(ss / D + eps);
-    float dot = 0.f;
-    if (normed) {
-      float gv[8];
-      load8_f32(g + e0, gv);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        xh[i] *= r;
-        if (h < Hq) accq[i] += d[i] * xh[i]; else acck[i] += d[i] * xh[i];
-        d[i] *= gv[i];
-        dot += d[i] * xh[i];
+    bool have_cs = false;
+    if (cache) {
+      const int64_t p = pos[row % T];
+      if (p >= 0 && p < cache_len) {
+        const float* cr = cache + (size_t)p * D;
+        load8_f32(cr + eh, c); load8_f32(cr + half + eh, sn);
+        have_cs = true;
       }
     }
-    dot = group_sum<D>(dot) / D;
-    if (normed) {
+    const size_t rbase = row * (size_t)H * D;
+    for (int h0 = 0; h0 < H; h0 += VPW * U) {
+      uint4 rawd[U], rawx[U];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) d[i] = r * (d[i] - xh[i] * dot);
+      for (int u = 0; u < U; ++u) {
+        const int h = h0 + u * VPW + hv;
+        const bool live = h < H;
+        const bool normed = live && h < Hq + Hkv && (h < Hq ? gq != nullptr : gk != nullptr);
+        rawd[u] = live ? *(const uint4*)(dout + rbase + (size_t)h * D + e0) : make_uint4(0, 0, 0, 0);
+        rawx[u] = normed ? *(const uint4*)(in + rbase + (size_t)h * D + e0) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int h = h0 + u * VPW + hv;
+        const bool live = h < H;
+        const bool rot = live && h < Hq + Hkv;
+        const bool isq = h < Hq;
+        const bool normed = rot && (isq ? gq != nullptr : gk != nullptr);
+        float d[8], xh[8];
+        unpack8(rawd[u], d);
+        unpack8(rawx[u], xh);
+        // every shuffle below is executed by the whole warp: lane groups of one warp may hold different kinds of heads
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, d[i], GL / 2);
+          if (rot && have_cs) d[i] = second ? d[i] * c[i] - other * sn[i] : d[i] * c[i] + other * sn[i];   // transpose of the rotation
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += xh[i] * xh[i];
+        ss = group_sum<D>(ss);
+        const float r = rsqrtf(ss / D + eps);
+        float dot = 0.f;
+        if (normed) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            xh[i] *= r;
+            if (isq) accq[i] += d[i] * xh[i]; else acck[i] += d[i] * xh[i];
+            d[i] *= isq ? gqv[i] : gkv[i];
+            dot += d[i] * xh[i];
+          }
+        }
+        dot = group_sum<D>(dot) / D;
+        if (normed) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) d[i] = r * (d[i] - xh[i] * dot);
+        }
+        if (live) *(uint4*)(din + rbase + (size_t)h * D + e0) = pack8(d);
+      }
     }
-    if (live) *(uint4*)(din + w * D + e0) = pack8(d);
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) { atomicAdd(&sg[0][e0 + i], accq[i]); atomicAdd(&sg[1][e0 + i], acck[i]); }
@@ -854,7 +856,7 @@ extern "C" int cpb_qk_norm_rope_fwd(const void* in, void* out, const float* gq, 
                                     const int64_t* pos, float* rstd, long rows, int T, int Hq, int Hkv, int D,
                                     float eps, int cache_len, int* status, cudaStream_t stream) {
   if (rows <= 0) return CPB_OK;
-  const int grid = grid_for((size_t)rows * (Hq + 2 * Hkv) / (256 / D) + 1, 8);      // a warp covers 256/D vectors per pass
+  const int grid = grid_for((size_t)rows, 8);      // one warp per token row, eight warps per block
   if (D == 64) qk_norm_rope_fwd_kernel<64><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, gq, gk, cache, pos, rstd, (size_t)rows, T, Hq, Hkv, eps, cache_len, status);
   else if (D == 128) qk_norm_rope_fwd_kernel<128><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, gq, gk, cache, pos, rstd, (size_t)rows, T, Hq, Hkv, eps, cache_len, status);
   else return set_error(CPB_ERR_ARG, "qk_norm_rope: head_dim %d not in {64,128}", D);
@@ -864,7 +866,7 @@ extern "C" int cpb_qk_norm_rope_bwd(const void* in, const void* dout, void* din,
                                     const float* cache, const int64_t* pos, float* dgq, float* dgk, long rows, int T,
                                     int Hq, int Hkv, int D, float eps, int cache_len, cudaStream_t stream) {
   if (rows <= 0) return CPB_OK;
-  const int grid = grid_for((size_t)rows * (Hq + 2 * Hkv) / (256 / D) + 1, 8, 4);
+  const int grid = grid_for((size_t)rows, 8, 4);
   if (D == 64) qk_norm_rope_bwd_kernel<64><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, (const __nv_bfloat16*)dout, (__nv_bfloat16*)din, gq, gk, cache, pos, dgq, dgk, (size_t)rows, T, Hq, Hkv, eps, cache_len);
   else if (D == 128) qk_norm_rope_bwd_kernel<128><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, (const __nv_bfloat16*)dout, (__nv_bfloat16*)din, gq, gk, cache, pos, dgq, dgk, (size_t)rows, T, Hq, Hkv, eps, cache_len);
   else return set_error(CPB_ERR_ARG, "qk_norm_rope: head_dim %d not in {64,128}", D);

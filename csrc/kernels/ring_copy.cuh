@@ -33,13 +33,17 @@ __device__ __forceinline__ void ring_copy_cta(const CopySeg* __restrict__ segs, 
       cur = seg.chunk;
     }
     const long stride = (long)n_ctas * blockDim.x;
-    long i = (long)cta * blockDim.x + threadIdx.x;
-    // four independent loads in flight per thread
-    for (; i + 3 * stride < seg.n16; i += 4 * stride) {
-      const uint4 a = seg.src[i], b = seg.src[i + stride], c = seg.src[i + 2 * stride], d = seg.src[i + 3 * stride];
-      seg.dst[i] = a; seg.dst[i + stride] = b; seg.dst[i + 2 * stride] = c; seg.dst[i + 3 * stride] = d;
+    // eight independent peer loads in flight per thread (the tail of a segment included) before the first store
+    constexpr int U = 8;
+    for (long i = (long)cta * blockDim.x + threadIdx.x; i < seg.n16; i += U * stride) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i + u * stride < seg.n16) v[u] = seg.src[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i + u * stride < seg.n16) seg.dst[i + u * stride] = v[u];
     }
-    for (; i < seg.n16; i += stride) seg.dst[i] = seg.src[i];
   }
   if (cur >= 0) ring_copy_arrive(ready, cur);
 }
