@@ -1,8 +1,9 @@
 // Flash-attention forward for sm_100a: S = Q K^T and O += P V on tcgen05 tensor cores with S, P and O
-// resident in tensor memory; K/V tiles streamed by TMA (no multicast) through a 2-stage ring; online
-// softmax with lazy rescaling in eight softmax warps (two threads per query row, 64 key columns each, row
-// maxima exchanged through shared memory), so each scheduler has enough warps to hide MUFU and tensor-memory
-// latency.
+// resident in tensor memory; K tiles streamed by TMA (no multicast) through a 3-stage and V tiles through a
+// 2-stage ring; online softmax with lazy rescaling in eight softmax warps (two threads per query row, 64 key
+// columns each, row maxima exchanged through shared memory), so each scheduler has enough warps to hide MUFU
+// and tensor-memory latency.  The exponentials of a tile are computed into registers before the wait for the
+// previous tile's P V product, so the tensor core's latency is off the softmax warps' per-tile chain.
 //
 // One kernel serves every attention mode of the framework:
 //   * local causal / non-causal attention with GQA (Ulysses, world size 1);
