@@ -228,3 +228,75 @@ def test_longrope_factor_file_reference_layout(tmp_path):
             R.parse_longrope_factors(str(p), 4)
     p.write_text("n_hat=1\ns=4\nsearch_len=64\n1.0 2.0 3.0 4.0\n")      # the older key=value form still loads
     assert R.parse_longrope_factors(str(p), 4) == ([1.0, 2.0, 3.0, 4.0], 1, 4, 64)
+
+
+# ----------------------------------------------------------------------------- sharded optimiser plan
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+def test_shard_plan_partitions_every_bucket(world):
+    """Every flat index has exactly one owner, owner boundaries are multiples of 8 elements, the shard buffers of one rank
+    are the concatenation of its padded runs, and the device kernels' ownership rule (element offset inside the bucket divided
+    by ``per``: csrc/kernels/comm.cu, reduce_scatter_f32_kernel / allgather_pull_kernel) names the same owner."""
+    from context_parallelism_b200.ops.optim import ShardPlan, plan_buckets
+    sizes = [64 * 3, 64 * 10, 64, 64 * 7, 64 * 2, 64 * 33]
+    entries, off = [], 0
+    for i, n in enumerate(sizes):
+        entries.append((f"p{i}", None, off, n))
+        off += n
+    buckets = plan_buckets(entries, off, bucket_elems=64 * 9)
+    assert buckets[0][0] == 0 and buckets[-1][1] == off
+    assert all(a[1] == b[0] for a, b in zip(buckets, buckets[1:]))             # contiguous, cut at parameter boundaries
+    owner = [-1] * off
+    for r in range(world):
+        plan = ShardPlan(buckets, world, r)
+        runs = plan.owned()
+        assert runs == sorted(runs)
+        for a, c, sb in runs:
+            assert a % 8 == 0 and sb % 8 == 0 and 0 <= sb and sb + (c - a) <= plan.shard_total
+            for e in range(a, c):
+                assert owner[e] == -1
+                owner[e] = r
+        for (s, n, per, shard_off), (a, c, sb) in zip([b for b in plan.buckets if b[0] + r * b[2] < b[0] + b[1]], runs):
+            assert per % 8 == 0 and per * world >= n and sb == shard_off and a == s + r * per
+    assert all(o >= 0 for o in owner)
+    plan = ShardPlan(buckets, world, 0)
+    for s, n, per, _ in plan.buckets:
+        for e in range(s, s + n, 5):
+            assert owner[e] == (e - s) // per
+
+
+@pytest.mark.parametrize("N", [1, 2, 4, 8])
+@pytest.mark.parametrize("lb", [True, False])
+def test_ring_chunk_tables_are_inverse(N, lb):
+    """``ring_rank_chunks`` and ``ring_chunk_owner`` describe the same assignment of the 2N position-ordered chunks
+    (head-tail balanced: rank r holds chunks r and 2N-1-r, context_parallel/HeadTailLoadBalancer.h:46-64; contiguous: 2r, 2r+1)."""
+    from context_parallelism_b200.parallel.fused import ring_chunk_owner, ring_rank_chunks
+    seen = set()
+    for r in range(N):
+        chunks = ring_rank_chunks(r, N, lb)
+        assert len(chunks) == 2
+        for half, c in enumerate(chunks):
+            assert ring_chunk_owner(c, N, lb) == (r, half)
+            seen.add(c)
+    assert seen == set(range(2 * N))
+    if lb:
+        # causal work per rank is equal: chunk c attends to c + 1 chunks (itself included)
+        work = [sum(c + 1 for c in ring_rank_chunks(r, N, True)) for r in range(N)]
+        assert len(set(work)) == 1
+
+
+@pytest.mark.parametrize("m_tiles,n_blocks,band", [(1, 1, 8), (11, 32, 8), (64, 8, 8), (5, 3, 1), (9, 7, 4), (32, 32, 8)])
+def test_pair_gemm_band_order_visits_every_tile_once(m_tiles, n_blocks, band):
+    """The tile order of the CTA-pair GEMM (csrc/kernels/gemm2.cu, pair_tile_coords): bands of ``band`` pair-rows swept along
+    N with rows fastest, the last band possibly shorter.  Restated here; the device code is checked against cuBLAS-free fp32
+    matmul on a ragged shape in tests/test_gpu_kernels.py::test_gemm_pair_banded_order."""
+    def coords(tile):
+        per_band = band * n_blocks
+        b, idx = divmod(tile, per_band)
+        rows = min(band, m_tiles - b * band)
+        nb, r = divmod(idx, rows)
+        return b * band + r, nb
+    got = [coords(t) for t in range(m_tiles * n_blocks)]
+    assert sorted(got) == [(m, n) for m in range(m_tiles) for n in range(n_blocks)]
+    # consecutive tiles of a full band share a column of B (rows fastest)
+    if m_tiles >= band > 1:
+        assert [c[1] for c in got[:band]] == [0] * band and [c[0] for c in got[:band]] == list(range(band))
