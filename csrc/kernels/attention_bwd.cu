@@ -566,10 +566,14 @@ extern "C" int cpb_flash_bwd(const void* q, const void* k, const void* v, const 
   p.lse2 = lse2; p.delta = delta; p.q_pos = q_pos; p.dq = dq; p.dk = dk; p.dv = dv;
   p.dkv_f32_accumulate = dkv_f32_accumulate; p.status = status;
   p.route_k = route_k; p.route_v = route_v; p.route_rows = route_rows; p.route_tl = route_tl;
-  {
+  // diagnostic switch, read once per process and announced when set
+  static const bool skip_dq = [] {
     const char* e = getenv("CPB_BWD_SKIP_DQ");
-    p.debug_skip_dq = (e != nullptr && e[0] == '1');
-  }
+    const bool on = e != nullptr && e[0] == '1';
+    if (on) fprintf(stderr, "CPB_BWD_SKIP_DQ=1: the attention backward does NOT produce dQ (timing experiment only)\n");
+    return on;
+  }();
+  p.debug_skip_dq = skip_dq;
   if (dkv_f32_accumulate == 2 && (route_k == nullptr || route_v == nullptr || route_rows <= 0))
     return set_error(CPB_ERR_ARG, "flash_bwd: routed dK/dV needs route tables");
   dim3 grid((Tk + FB_T - 1) / FB_T, Hkv, B);

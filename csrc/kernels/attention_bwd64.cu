@@ -617,7 +617,12 @@ extern "C" int cpb_flash_bwd64(const void* q, const void* k, const void* v, cons
   p.dk = dk; p.dv = dv; p.dkv_mode = dkv_mode; p.status = status;
   p.route_k = route_k; p.route_v = route_v; p.route_rows = route_rows; p.route_tl = route_tl;
   // diagnostic switches and the tuning knob are read once per process, not per launch
-  static const bool skip_dq = [] { const char* e = getenv("CPB_BWD_SKIP_DQ"); return e != nullptr && e[0] == '1'; }();
+  static const bool skip_dq = [] {
+    const char* e = getenv("CPB_BWD_SKIP_DQ");
+    const bool on = e != nullptr && e[0] == '1';
+    if (on) fprintf(stderr, "CPB_BWD_SKIP_DQ=1: the attention backward does NOT produce dQ (timing experiment only)\n");
+    return on;
+  }();
   static const bool want_prof = [] { const char* e = getenv("CPB_BWD_PROF"); return e != nullptr && e[0] == '1'; }();
   static const int poly = [] { const char* e = getenv("CPB_BWD64_POLY"); return e ? atoi(e) : B64_POLY; }();
   p.debug_skip_dq = skip_dq;
